@@ -1,0 +1,158 @@
+// Memory-bound row kernels: embedding gather, RMSNorm (optionally through a row
+// index), SiLU-gate multiply, in-place add and dtype casts.
+//
+// Formulas follow the reference: the norm squares, averages, adds eps, takes the
+// reciprocal square root and scales in float32, rounds to the activation dtype and
+// only then multiplies by the weight (qil/model.py:21-23); the gate is
+// silu(gate) rounded to the activation dtype, times up (qil/model.py:71).
+#include "common.cuh"
+
+QIL_ERROR_STORAGE
+
+// ---------------------------------------------------------------- embedding
+template <typename T, typename W>
+__global__ void embed_gather_kernel(const W* __restrict__ table, const int* __restrict__ ids,
+                                    T* __restrict__ out, int width, int vocab) {
+    const int row = blockIdx.x;
+    int id = ids[row];
+    // Host code validates ids; clamp so that a bad id can never read out of bounds.
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const W* src = table + (size_t)id * width;
+    T* dst = out + (size_t)row * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(to_f32<W>(src[i]));
+}
+
+extern "C" int qil_embed_gather(const void* table, int table_dtype, const int* ids, void* out,
+                                int out_dtype, int n_rows, int width, int vocab, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width <= 0 || vocab <= 0) QIL_REFUSE("embed_gather: width %d vocab %d", width, vocab);
+    QIL_DISPATCH_2(out_dtype, table_dtype,
+        embed_gather_kernel<T, W><<<n_rows, 256, 0, stream>>>((const W*)table, ids, (T*)out, width, vocab));
+    QIL_CHECK_LAUNCH();
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// One block per output row.  rows == nullptr: row r reads x[r]; else x[rows[r]].
+template <typename T, typename W>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, const W* __restrict__ weight,
+                               const int* __restrict__ rows, T* __restrict__ out,
+                               int width, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src_row = rows ? rows[r] : r;
+    const T* src = x + (size_t)src_row * width;
+    T* dst = out + (size_t)r * width;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = to_f32<T>(src[i]);
+        sq += v * v;
+    }
+    sq = block_sum(sq, scratch);
+    const float scale = 1.0f / sqrtf(sq / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float normed = round_to<T>(to_f32<T>(src[i]) * scale);
+        dst[i] = from_f32<T>(normed * to_f32<W>(weight[i]));
+    }
+}
+
+extern "C" int qil_rmsnorm(const void* x, const void* weight, const int* rows, void* out,
+                           int n_rows, int width, float eps, int act_dtype, int weight_dtype,
+                           cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width <= 0) QIL_REFUSE("rmsnorm: width %d", width);
+    QIL_DISPATCH_2(act_dtype, weight_dtype,
+        rmsnorm_kernel<T, W><<<n_rows, 256, 0, stream>>>((const T*)x, (const W*)weight, rows, (T*)out, width, eps));
+    QIL_CHECK_LAUNCH();
+}
+
+// ---------------------------------------------------------------- SiLU(gate) * up
+// gate_up: [n_rows, 2 * width] (gate columns first, then up); out: [n_rows, width].
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width,
+                                size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const size_t row = i / width;
+        const int col = (int)(i - row * width);
+        const float g = to_f32<T>(gate_up[row * 2 * width + col]);
+        const float u = to_f32<T>(gate_up[row * 2 * width + width + col]);
+        const float act = round_to<T>(g / (1.0f + expf(-g)));
+        out[i] = from_f32<T>(act * u);
+    }
+}
+
+// 8 bf16 values per thread when the width allows 16-byte accesses.
+__global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out,
+                                       int width, size_t total_vec) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int vec_per_row = width / 8;
+    for (; i < total_vec; i += stride) {
+        const size_t row = i / vec_per_row;
+        const int col = (int)(i - row * vec_per_row) * 8;
+        const uint4 g4 = *reinterpret_cast<const uint4*>(gate_up + row * 2 * width + col);
+        const uint4 u4 = *reinterpret_cast<const uint4*>(gate_up + row * 2 * width + width + col);
+        const bf16* g = reinterpret_cast<const bf16*>(&g4);
+        const bf16* u = reinterpret_cast<const bf16*>(&u4);
+        uint4 o4;
+        bf16* o = reinterpret_cast<bf16*>(&o4);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float gv = __bfloat162float(g[k]);
+            const float act = round_to<bf16>(gv / (1.0f + expf(-gv)));
+            o[k] = __float2bfloat16_rn(act * __bfloat162float(u[k]));
+        }
+        *reinterpret_cast<uint4*>(out + row * width + col) = o4;
+    }
+}
+
+extern "C" int qil_silu_mul(const void* gate_up, void* out, int n_rows, int width, int act_dtype,
+                            cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width <= 0) QIL_REFUSE("silu_mul: width %d", width);
+    const size_t total = (size_t)n_rows * width;
+    if (act_dtype == QIL_BF16 && width % 8 == 0 && ((uintptr_t)gate_up % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        const size_t total_vec = total / 8;
+        const int blocks = (int)((total_vec + 255) / 256 < 148 * 16 ? (total_vec + 255) / 256 : 148 * 16);
+        silu_mul_bf16x8_kernel<<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, width, total_vec);
+        QIL_CHECK_LAUNCH();
+    }
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    QIL_DISPATCH_1(act_dtype,
+        silu_mul_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, width, total));
+    QIL_CHECK_LAUNCH();
+}
+
+// ---------------------------------------------------------------- x += y (float32 sum, one rounding)
+template <typename T>
+__global__ void add_inplace_kernel(T* __restrict__ x, const T* __restrict__ y, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) x[i] = from_f32<T>(to_f32<T>(x[i]) + to_f32<T>(y[i]));
+}
+
+extern "C" int qil_add_inplace(void* x, const void* y, long long total, int act_dtype, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    QIL_DISPATCH_1(act_dtype,
+        add_inplace_kernel<T><<<blocks, 256, 0, stream>>>((T*)x, (const T*)y, (size_t)total));
+    QIL_CHECK_LAUNCH();
+}
+
+// ---------------------------------------------------------------- dtype cast (src dtype -> dst dtype)
+template <typename T, typename W>
+__global__ void cast_kernel(const W* __restrict__ src, T* __restrict__ dst, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) dst[i] = from_f32<T>(to_f32<W>(src[i]));
+}
+
+extern "C" int qil_cast(const void* src, int src_dtype, void* dst, int dst_dtype, long long total,
+                        cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    QIL_DISPATCH_2(dst_dtype, src_dtype,
+        cast_kernel<T, W><<<blocks, 256, 0, stream>>>((const W*)src, (T*)dst, (size_t)total));
+    QIL_CHECK_LAUNCH();
+}

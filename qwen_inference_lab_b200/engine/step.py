@@ -1,0 +1,196 @@
+"""The step function: one flat batch of (request, its next tokens) through the model.
+
+A step takes any mix of prompt portions and single decoded tokens, cut anywhere,
+runs exactly those tokens as one batch against the cache that earlier steps
+left, and returns float32 logits at the places that were asked for.  The
+reference runs a prefill chunk of one request (qil/model.py:110-134) or one token
+of several requests (qil/model.py:136-157) per forward and several forwards per
+step (qil/engine.py:63-86); here every step is one pass over the layers.
+
+The batch is described to the kernels by int32 arrays in one device buffer,
+uploaded with a single copy per step (see :class:`StepContext` for the fields).
+Steps made only of single tokens are recorded into CUDA graphs, one per batch
+size and context bucket, and replayed after the metadata upload.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..parts.base import StepContext
+from ..utils.staging import PinnedRing
+
+QUERY_TILE = 64          # tokens per query tile of the prompt-portion attention kernel
+
+
+class StepError(ValueError):
+    """A batch that cannot run: unknown request, bad token, position beyond the context..."""
+
+
+@dataclass
+class StepEntry:
+    request_id: object
+    tokens: list
+    want: list = field(default_factory=list)   # indices into ``tokens`` whose logits are returned
+
+
+def _align4(n):
+    return (n + 3) & ~3
+
+
+class StepRunner:
+    def __init__(self, model, cache, *, max_step_tokens=4096, use_graphs=True, graph_max_batch=256):
+        self.model, self.cache = model, cache
+        self.device = model.device
+        self.views = cache.views(model.order)
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and model.is_graph_safe()
+        self.graph_max_batch = graph_max_batch
+        self._capacity = 0
+        self._meta_dev = None
+        self._ring = PinnedRing() if self.device.type == "cuda" else None
+        self._graphs: dict = {}
+        self._graph_pool = None
+        self._reserve(8 * max_step_tokens + 8 * cache.max_requests + 64)
+        self.steps_run = 0
+        self.kernel_launch_estimate = 0
+
+    def _reserve(self, ints):
+        if ints <= self._capacity:
+            return
+        self._capacity = int(ints)
+        self._meta_dev = torch.zeros(self._capacity, dtype=torch.int32, device=self.device)
+        self._graphs.clear()     # recorded graphs point into the old buffer
+
+    # ------------------------------------------------------------------ the batch
+    def _validate(self, entries):
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        vocab = self.model.vocab_size
+        for entry in entries:
+            if entry.request_id in seen:
+                raise StepError(f"request {entry.request_id!r} appears twice in one step")
+            seen.add(entry.request_id)
+            if entry.request_id not in self.cache.rows:
+                raise StepError(f"request {entry.request_id!r} has not been admitted to the cache")
+            tokens = entry.tokens
+            if len(tokens) == 0:
+                raise StepError(f"request {entry.request_id!r} brings no tokens")
+            if any(type(t) is not int or not 0 <= t < vocab for t in tokens):
+                raise StepError(f"request {entry.request_id!r}: token ids must be integers in [0, {vocab})")
+            start = self.cache.written(entry.request_id)
+            if start + len(tokens) > self.model.max_positions:
+                raise StepError(f"request {entry.request_id!r} exceeds the model's {self.model.max_positions} positions")
+            if any(type(w) is not int or not 0 <= w < len(tokens) for w in entry.want):
+                raise StepError(f"request {entry.request_id!r}: wanted places must index its tokens of this step")
+
+    def _describe(self, entries):
+        """Host arrays of the batch, packed into one int32 vector with section offsets."""
+        lens = np.array([len(e.tokens) for e in entries], dtype=np.int64)
+        starts = np.array([self.cache.written(e.request_id) for e in entries], dtype=np.int64)
+        rows = np.array([self.cache.row(e.request_id) for e in entries], dtype=np.int64)
+        n, s = int(lens.sum()), len(entries)
+        seg_start = np.zeros(s, dtype=np.int64)
+        np.cumsum(lens[:-1], out=seg_start[1:])
+        token_ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=n)
+        seg_of_token = np.repeat(np.arange(s), lens)
+        positions = np.arange(n) - seg_start[seg_of_token] + starts[seg_of_token]
+        token_row = rows[seg_of_token]
+        logit_rows = np.array([seg_start[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int64)
+        tile_seg, tile_off = [], []
+        for i in np.nonzero(lens > 1)[0]:
+            for off in range(0, int(lens[i]), QUERY_TILE):
+                tile_seg.append(i)
+                tile_off.append(off)
+        decode_seg = np.nonzero(lens == 1)[0]
+        sections = [("token_ids", token_ids), ("positions", positions), ("token_row", token_row),
+                    ("seg_row", rows), ("seg_start", seg_start), ("seg_len", lens), ("seg_pos0", starts),
+                    ("logit_rows", logit_rows), ("tile_seg", np.array(tile_seg, dtype=np.int64)),
+                    ("tile_off", np.array(tile_off, dtype=np.int64)), ("decode_seg", decode_seg)]
+        offsets, total = {}, 0
+        for name, values in sections:
+            offsets[name] = (total, len(values))
+            total += _align4(max(len(values), 1))
+        packed = np.zeros(total, dtype=np.int32)
+        for name, values in sections:
+            begin, count = offsets[name]
+            packed[begin:begin + count] = values
+        host = dict(seg_row=rows, seg_start=seg_start, seg_len=lens, seg_pos0=starts)
+        return packed, offsets, host, n, s, int((starts + lens).max())
+
+    def _context(self, offsets, host, n, s, max_context):
+        def section(name):
+            begin, count = offsets[name]
+            return self._meta_dev[begin:begin + count]
+        return StepContext(
+            n_tokens=n, n_segments=s, dtype=self.model.dtype, device=self.device,
+            token_ids=section("token_ids"), positions=section("positions"), token_row=section("token_row"),
+            seg_row=section("seg_row"), seg_start=section("seg_start"), seg_len=section("seg_len"),
+            seg_pos0=section("seg_pos0"), n_tiles=offsets["tile_seg"][1], tile_seg=section("tile_seg"),
+            tile_off=section("tile_off"), n_decode=offsets["decode_seg"][1], decode_seg=section("decode_seg"),
+            max_context=max_context, h_seg_row=host["seg_row"], h_seg_start=host["seg_start"],
+            h_seg_len=host["seg_len"], h_seg_pos0=host["seg_pos0"])
+
+    def _upload(self, packed):
+        self._reserve(len(packed))
+        if self.device.type != "cuda":
+            self._meta_dev[:len(packed)] = torch.from_numpy(packed)
+            return
+        stage = self._ring.acquire(packed.nbytes).view(torch.int32)[:len(packed)]
+        stage.numpy()[:] = packed
+        self._meta_dev[:len(packed)].copy_(stage, non_blocking=True)
+        self._ring.commit()
+
+    # ------------------------------------------------------------------ running
+    def run(self, entries) -> torch.Tensor | None:
+        """Run one step; float32 logits [wanted, vocab] in the order of entries and ``want``.
+
+        Pages for the new tokens are taken first, the cache's progress moves after the
+        layers have been queued.  On an exception the requests of the batch may hold
+        partly written pages: the caller retires them (qil/engine.py:87-93).
+        """
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        self._validate(entries)
+        for entry in entries:
+            self.cache.ensure(entry.request_id, self.cache.written(entry.request_id) + len(entry.tokens))
+        packed, offsets, host, n, s, max_context = self._describe(entries)
+        self.cache.flush_tables()
+        self._upload(packed)
+        all_single = offsets["tile_seg"][1] == 0 and offsets["logit_rows"][1] == n \
+            and all(e.want == [0] for e in entries)
+        if self.use_graphs and all_single and n <= self.graph_max_batch:
+            logits = self._run_graph(offsets, host, n, s, max_context)
+        else:
+            ctx = self._context(offsets, host, n, s, max_context)
+            begin, count = offsets["logit_rows"]
+            logits = self.model.forward(ctx, self.views, self._meta_dev[begin:begin + count] if count else None)
+        for entry in entries:
+            self.cache.advance(entry.request_id, self.cache.written(entry.request_id) + len(entry.tokens))
+        self.steps_run += 1
+        return logits
+
+    def _run_graph(self, offsets, host, n, s, max_context):
+        bucket = 512
+        while bucket < max_context:
+            bucket *= 2
+        key = (n, bucket)
+        record = self._graphs.get(key)
+        if record is None:
+            ctx = self._context(offsets, host, n, s, bucket)
+            begin, count = offsets["logit_rows"]
+            logit_rows = self._meta_dev[begin:begin + count]
+            # one eager run first: libraries set up their workspaces outside the recording
+            self.model.forward(ctx, self.views, logit_rows)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                logits = self.model.forward(ctx, self.views, logit_rows)
+            record = (graph, logits)
+            self._graphs[key] = record
+        graph, logits = record
+        graph.replay()
+        return logits

@@ -1,0 +1,249 @@
+"""Python face of the CUDA kernels: argument checks, then one C call per kernel.
+
+Every function launches on torch's current CUDA stream and returns without
+synchronising.  Tensors must live on the GPU and be contiguous; a wrong dtype,
+shape or device raises before anything is launched.  There is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "attention_generic.cu", "sampling.cu"]
+
+_core = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def core():
+    global _core
+    if _core is None:
+        _core = build.load("qil_core", CORE_SOURCES)
+    return _core
+
+
+def dtype_code(dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _check(lib, code, what):
+    if code != 0:
+        raise KernelError(f"{what}: {lib.qil_last_error().decode()} (code {code})")
+
+
+def _p(tensor):
+    return c_void_p(tensor.data_ptr()) if tensor is not None else c_void_p(0)
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(tensor, name, dtype=None, ndim=None):
+    if not isinstance(tensor, torch.Tensor) or not tensor.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not tensor.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+    if ndim is not None and tensor.ndim != ndim:
+        raise KernelError(f"{name} must have {ndim} dimensions, got {tuple(tensor.shape)}")
+
+
+def embed_gather(table, ids, out):
+    """out[r] = table[ids[r]] cast to out's dtype.  table [V,H]; ids int32 [N]; out [N,H]."""
+    _need(table, "table", ndim=2); _need(ids, "ids", torch.int32, 1); _need(out, "out", ndim=2)
+    if out.shape != (ids.shape[0], table.shape[1]):
+        raise KernelError(f"embed_gather: out {tuple(out.shape)} for ids {tuple(ids.shape)} table {tuple(table.shape)}")
+    lib = core()
+    _check(lib, lib.qil_embed_gather(_p(table), c_int(dtype_code(table.dtype)), _p(ids), _p(out),
+                                     c_int(dtype_code(out.dtype)), c_int(ids.shape[0]), c_int(table.shape[1]),
+                                     c_int(table.shape[0]), _stream()), "embed_gather")
+    return out
+
+
+def rmsnorm(x, weight, eps, out=None, rows=None):
+    """RMSNorm over the last dimension; with ``rows`` (int32) only those rows, in that order."""
+    _need(x, "x", ndim=2); _need(weight, "weight", ndim=1)
+    width = x.shape[1]
+    if weight.shape[0] != width:
+        raise KernelError(f"rmsnorm: weight of {weight.shape[0]} for width {width}")
+    n_rows = x.shape[0] if rows is None else rows.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+    if out is None:
+        out = torch.empty((n_rows, width), dtype=x.dtype, device=x.device)
+    _need(out, "out", x.dtype, 2)
+    if out.shape != (n_rows, width):
+        raise KernelError("rmsnorm: out has the wrong shape")
+    lib = core()
+    _check(lib, lib.qil_rmsnorm(_p(x), _p(weight), _p(rows), _p(out), c_int(n_rows), c_int(width),
+                                c_float(eps), c_int(dtype_code(x.dtype)), c_int(dtype_code(weight.dtype)),
+                                _stream()), "rmsnorm")
+    return out
+
+
+def silu_mul(gate_up, out=None):
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _need(gate_up, "gate_up", ndim=2)
+    if gate_up.shape[1] % 2:
+        raise KernelError("silu_mul: the input's width must be even (gate columns then up columns)")
+    width = gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((gate_up.shape[0], width), dtype=gate_up.dtype, device=gate_up.device)
+    _need(out, "out", gate_up.dtype, 2)
+    lib = core()
+    _check(lib, lib.qil_silu_mul(_p(gate_up), _p(out), c_int(gate_up.shape[0]), c_int(width),
+                                 c_int(dtype_code(gate_up.dtype)), _stream()), "silu_mul")
+    return out
+
+
+def add_inplace(x, y):
+    _need(x, "x"); _need(y, "y", x.dtype)
+    if x.shape != y.shape:
+        raise KernelError("add_inplace: shapes differ")
+    lib = core()
+    _check(lib, lib.qil_add_inplace(_p(x), _p(y), c_longlong(x.numel()), c_int(dtype_code(x.dtype)), _stream()),
+           "add_inplace")
+    return x
+
+
+def cast(src, dtype, out=None):
+    _need(src, "src")
+    if out is None:
+        out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    _need(out, "out", dtype)
+    lib = core()
+    _check(lib, lib.qil_cast(_p(src), c_int(dtype_code(src.dtype)), _p(out), c_int(dtype_code(dtype)),
+                             c_longlong(src.numel()), _stream()), "cast")
+    return out
+
+
+def gemm_f32(a, weight, bias=None, residual=None, out=None):
+    """out = a @ weight.T (+ bias) (+ residual), float32 accumulation on the CUDA cores.
+
+    a [M,K] and out [M,N] share a dtype; weight [N,K] and bias [N] share another.
+    ``residual`` may be ``out`` itself.
+    """
+    _need(a, "a", ndim=2); _need(weight, "weight", ndim=2)
+    m, k = a.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"gemm_f32: a {tuple(a.shape)} against weight {tuple(weight.shape)}")
+    if bias is not None:
+        _need(bias, "bias", weight.dtype, 1)
+        if bias.shape[0] != n:
+            raise KernelError("gemm_f32: bias has the wrong length")
+    if out is None:
+        out = torch.empty((m, n), dtype=a.dtype, device=a.device)
+    _need(out, "out", a.dtype, 2)
+    if out.shape != (m, n):
+        raise KernelError("gemm_f32: out has the wrong shape")
+    if residual is not None:
+        _need(residual, "residual", a.dtype, 2)
+        if residual.shape != (m, n):
+            raise KernelError("gemm_f32: residual has the wrong shape")
+    lib = core()
+    _check(lib, lib.qil_gemm_f32(_p(a), c_int(k), _p(weight), _p(bias), _p(residual), _p(out), c_int(m), c_int(n),
+                                 c_int(k), c_int(dtype_code(a.dtype)), c_int(dtype_code(weight.dtype)), _stream()),
+           "gemm_f32")
+    return out
+
+
+def qk_norm_rope_store(qkv, q_out, kv_cache, q_norm_w, k_norm_w, eps, rope_table, rotary_dim,
+                       positions, token_row, block_table, n_q_heads, n_kv_heads, head_dim, page_size):
+    """Norm and rotate q and k heads of ``qkv``, write q to ``q_out`` and k, v into ``kv_cache``.
+
+    qkv [N, (Hq + 2*Hkv) * D]; q_out [N, Hq*D]; kv_cache [pages, 2, Hkv, P, D] (one layer);
+    rope_table float32 [positions, rotary_dim] or None; block_table int32 [rows, max_pages].
+    With n_kv_heads == 0 only queries are processed (a layer that reads another layer's cache).
+    """
+    _need(qkv, "qkv", ndim=2); _need(q_out, "q_out", qkv.dtype, 2)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_q_heads + 2 * n_kv_heads) * head_dim or q_out.shape != (n, n_q_heads * head_dim):
+        raise KernelError("qk_norm_rope_store: qkv/q_out shapes do not match the head counts")
+    _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
+    num_pages = 0
+    if n_kv_heads:
+        _need(kv_cache, "kv_cache", qkv.dtype, 5); _need(block_table, "block_table", torch.int32, 2)
+        if tuple(kv_cache.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
+            raise KernelError(f"qk_norm_rope_store: cache layout {tuple(kv_cache.shape)}")
+        num_pages = kv_cache.shape[0]
+    norm_code = F32
+    if q_norm_w is not None:
+        _need(q_norm_w, "q_norm_w", ndim=1); _need(k_norm_w, "k_norm_w", q_norm_w.dtype, 1)
+        if q_norm_w.shape[0] != head_dim or k_norm_w.shape[0] != head_dim:
+            raise KernelError("qk_norm_rope_store: norm weights must have head_dim elements")
+        norm_code = dtype_code(q_norm_w.dtype)
+    table_rows = 0
+    if rope_table is not None:
+        _need(rope_table, "rope_table", torch.float32, 2)
+        if rope_table.shape[1] != rotary_dim:
+            raise KernelError("qk_norm_rope_store: rope table width must equal rotary_dim")
+        table_rows = rope_table.shape[0]
+    lib = core()
+    _check(lib, lib.qil_qk_norm_rope_store(
+        _p(qkv), _p(q_out), _p(kv_cache if n_kv_heads else None), _p(q_norm_w), _p(k_norm_w), c_int(norm_code),
+        c_float(eps), _p(rope_table), c_int(rotary_dim if rope_table is not None else 0), c_int(table_rows),
+        _p(positions), _p(token_row), _p(block_table if n_kv_heads else None),
+        c_int(block_table.shape[1] if n_kv_heads else 0), c_int(n), c_int(n_q_heads), c_int(n_kv_heads),
+        c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(dtype_code(qkv.dtype)), _stream()),
+        "qk_norm_rope_store")
+    return q_out
+
+
+def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_heads, n_kv_heads,
+                      head_dim, page_size, window, scale):
+    """Causal GQA attention of every token over its request's pages (CUDA cores, float32 math)."""
+    _need(q, "q", ndim=2); _need(out, "out", q.dtype, 2); _need(kv_cache, "kv_cache", q.dtype, 5)
+    n = q.shape[0]
+    if q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
+        raise KernelError("attention_generic: q/out shapes do not match the head counts")
+    if tuple(kv_cache.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
+        raise KernelError(f"attention_generic: cache layout {tuple(kv_cache.shape)}")
+    _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
+    _need(block_table, "block_table", torch.int32, 2)
+    lib = core()
+    _check(lib, lib.qil_attention_generic(
+        _p(q), _p(kv_cache), _p(out), _p(positions), _p(token_row), _p(block_table), c_int(block_table.shape[1]),
+        c_int(n), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
+        c_int(kv_cache.shape[0]), c_int(window), c_float(scale), c_int(dtype_code(q.dtype)), _stream()),
+        "attention_generic")
+    return out
+
+
+def sample_rows(logits, temperature=None, seed=None, counter=None, tokens=None, nonfinite=None):
+    """Choose one token per row of float32 ``logits`` [R,V]; returns (tokens, nonfinite) int32 [R].
+
+    temperature float32 [R] (0 = greedy), seed and counter int64 [R]; all optional (greedy).
+    """
+    _need(logits, "logits", torch.float32, 2)
+    rows, vocab = logits.shape
+    for name, t, dt in (("temperature", temperature, torch.float32), ("seed", seed, torch.int64),
+                        ("counter", counter, torch.int64)):
+        if t is not None:
+            _need(t, name, dt, 1)
+            if t.shape[0] != rows:
+                raise KernelError(f"sample_rows: {name} needs one entry per row")
+    if tokens is None:
+        tokens = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if nonfinite is None:
+        nonfinite = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    lib = core()
+    _check(lib, lib.qil_sample_rows(_p(logits), c_int(rows), c_int(vocab), c_longlong(logits.stride(0)),
+                                    _p(temperature), _p(seed), _p(counter), _p(tokens), _p(nonfinite), _stream()),
+           "sample_rows")
+    return tokens, nonfinite

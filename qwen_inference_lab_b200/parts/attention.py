@@ -1,0 +1,100 @@
+"""Causal grouped-query attention over paged keys and values.
+
+Per token: q, k, v projections (one stacked product), RMSNorm of every q and k
+head over head_dim, rotation of q and k by the token's absolute position, k and v
+written to the request's pages, softmax(q k^T * scale) over the keys up to the
+token's own position (inside the window, if one is set), times v, then the output
+projection (qil/model.py:48-69 for a chunk, :73-84 for single tokens; both are
+the same computation here, every token of the flat batch takes it).  Query head
+``h`` reads kv head ``h // (n_q_heads // n_kv_heads)`` (qil/paged_attention.py:21).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import KVCacheSpec, Mixer, Param
+from .linear import Linear, StackedLinear
+
+
+class GroupedQueryAttention(Mixer):
+    """Sizes and constants are arguments; ``names`` gives the checkpoint names.
+
+    names: dict with keys q, k, v, o (projection names, without ``.weight``) and,
+    when ``qk_norm_eps`` is not None, q_norm and k_norm.
+    ``reads_shared_cache=True`` builds a layer without k and v projections that
+    attends over pages another layer wrote (the model's order says which).
+    """
+    graph_safe = True
+
+    def __init__(self, hidden_size, n_q_heads, n_kv_heads, head_dim, *, names, bias=False,
+                 qk_norm_eps=None, position=None, window=0, scale=None, reads_shared_cache=False):
+        if n_q_heads % n_kv_heads:
+            raise ValueError(f"{n_q_heads} query heads do not divide into {n_kv_heads} kv heads")
+        self.hidden_size, self.head_dim = int(hidden_size), int(head_dim)
+        self.n_q_heads, self.n_kv_heads = int(n_q_heads), int(n_kv_heads)
+        self.window = int(window)
+        self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
+        self.qk_norm_eps = qk_norm_eps
+        self.position = position
+        self.reads_shared_cache = bool(reads_shared_cache)
+        pieces = [(names["q"], n_q_heads * head_dim)]
+        if not self.reads_shared_cache:
+            pieces += [(names["k"], n_kv_heads * head_dim), (names["v"], n_kv_heads * head_dim)]
+        self.qkv = StackedLinear(hidden_size, pieces, bias=bias)
+        self.out = Linear(n_q_heads * head_dim, hidden_size, name=names["o"], bias=bias)
+        self.q_norm = self.k_norm = None
+        self._norm_names = None
+        if qk_norm_eps is not None:
+            self.q_norm = Param((head_dim,), init="norm", std=0.05)
+            self.k_norm = Param((head_dim,), init="norm", std=0.05)
+            self._norm_names = (names["q_norm"] + ".weight", names["k_norm"] + ".weight")
+
+    def named_params(self):
+        if self._norm_names is None:
+            return {}
+        return {self._norm_names[0]: self.q_norm, self._norm_names[1]: self.k_norm}
+
+    def children(self):
+        parts = [self.qkv, self.out]
+        if self.position is not None:
+            parts.append(self.position)
+        return parts
+
+    def finalize(self, device, dtype):
+        super().finalize(device, dtype)
+        if self.q_norm is not None and self.q_norm.data.dtype != self.k_norm.data.dtype:
+            self.q_norm.data, self.k_norm.data = self.q_norm.data.float(), self.k_norm.data.float()
+
+    def cache_spec(self):
+        if self.reads_shared_cache:
+            return None
+        return KVCacheSpec(self.n_kv_heads, self.head_dim, self.window)
+
+    def forward(self, ctx, x, cache, residual=None):
+        """x [N, hidden] -> [N, hidden] (+ residual).  ``cache`` is a KVCacheView."""
+        n = x.shape[0]
+        n_kv = 0 if self.reads_shared_cache else self.n_kv_heads
+        qkv = self.qkv.forward(ctx, x)
+        q = ctx.empty((n, self.n_q_heads * self.head_dim))
+        table = self.position.table if self.position is not None else None
+        rotary_dim = self.position.rotary_dim if self.position is not None else 0
+        ops.qk_norm_rope_store(
+            qkv, q, cache.pages, self.q_norm.data if self.q_norm is not None else None,
+            self.k_norm.data if self.k_norm is not None else None,
+            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, table, rotary_dim,
+            ctx.positions, ctx.token_row, cache.block_table, self.n_q_heads, n_kv, self.head_dim,
+            cache.page_size)
+        attended = ctx.empty((n, self.n_q_heads * self.head_dim))
+        self._attend(ctx, q, cache, attended)
+        return self.out.forward(ctx, attended, residual=residual)
+
+    def _attend(self, ctx, q, cache, out):
+        from ..kernels import attention_mma
+        if q.dtype == torch.bfloat16 and attention_mma.supports(self.head_dim, self.n_q_heads, self.n_kv_heads):
+            attention_mma.attend(ctx, q, cache, out, self.n_q_heads, self.n_kv_heads, self.head_dim,
+                                 self.window, self.scale)
+            return
+        ops.attention_generic(q, cache.pages, out, ctx.positions, ctx.token_row, cache.block_table,
+                              self.n_q_heads, self.n_kv_heads, self.head_dim, cache.page_size,
+                              self.window, self.scale)

@@ -1,0 +1,158 @@
+"""What every part of a model is made of: parameters, cache needs, the step context.
+
+A model is a tree of parts.  A part owns its sizes and constants (given as
+arguments, never read from a global configuration), its parameters, and a
+``forward`` over the flat batch of tokens that one step brings.  No part knows
+which model it is in: the checkpoint names of its parameters are handed to it by
+the architecture's builder.
+
+Interfaces
+----------
+``Part``        ``named_params()`` (checkpoint name -> ``Param``), ``children()``,
+                ``finalize(device, dtype)`` after the weights are in.
+``Norm``        ``forward(ctx, x, rows=None) -> y`` over the last dimension.
+``PositionEncoding``  ``table`` (float32 ``[positions, rotary_dim]``: cosines then
+                sines) and ``rotary_dim``; mixers hand the table to their kernels.
+``Mixer``       ``cache_spec()`` (what it keeps per request: paged keys/values, a
+                fixed-size state, or nothing) and ``forward(ctx, x, cache) -> y``.
+``FeedForward`` ``forward(ctx, x, residual=None) -> y``.
+``Block``       ``forward(ctx, x, cache) -> x`` (arrangement of the above).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+
+class Param:
+    """One parameter tensor: shape, how random weights draw it, and the loaded data.
+
+    ``init`` is ``"normal"`` (N(0, std)), ``"norm"`` (1 + N(0, std)) or ``"zeros"``.
+    Several checkpoint names may point to one Param (tied embeddings).
+    """
+
+    __slots__ = ("shape", "init", "std", "data", "integer")
+
+    def __init__(self, shape, init="normal", std=0.02, integer=False):
+        self.shape = tuple(int(n) for n in shape)
+        self.init = init
+        self.std = std
+        self.integer = integer
+        self.data: torch.Tensor | None = None
+
+    def __repr__(self):
+        return f"Param{self.shape}"
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """Paged keys and values: ``kv_heads * head_dim`` of each per token.
+
+    ``window`` > 0 means that only the last ``window`` positions are ever read, so
+    pages that the window has passed are given back while the request lives.
+    """
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """A fixed-size state per request (``shape`` elements of ``dtype``), zeroed at admission."""
+    shape: tuple
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    """Base of all parts."""
+
+    #: True when ``forward`` only launches work on the current stream with no host
+    #: synchronisation and no data-dependent host control flow, so that a step made
+    #: of such parts may be recorded into a CUDA graph.
+    graph_safe = False
+
+    def named_params(self) -> dict:
+        """Checkpoint name -> Param for this part alone (children excluded)."""
+        return {}
+
+    def children(self) -> list:
+        return []
+
+    def all_named_params(self) -> dict:
+        result = dict(self.named_params())
+        for child in self.children():
+            for name, param in child.all_named_params().items():
+                if name in result and result[name] is not param:
+                    raise ValueError(f"two different parameters claim the name {name}")
+                result[name] = param
+        return result
+
+    def finalize(self, device, dtype) -> None:
+        """Called once after all parameters hold data; fuse or derive tensors here."""
+        for child in self.children():
+            child.finalize(device, dtype)
+
+    def is_graph_safe(self) -> bool:
+        return self.graph_safe and all(child.is_graph_safe() for child in self.children())
+
+
+class Norm(Part):
+    def forward(self, ctx, x, rows=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    rotary_dim = 0
+    table: torch.Tensor | None = None
+
+
+class Mixer(Part):
+    def cache_spec(self):
+        return None
+
+    def forward(self, ctx, x, cache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x, residual=None):
+        raise NotImplementedError
+
+
+@dataclass
+class StepContext:
+    """Everything a part may know about the step in flight.
+
+    The batch is flat: ``n_tokens`` tokens made of ``n_segments`` segments, one per
+    request, each a run of consecutive positions.  Device arrays are int32.
+    Host copies (``h_*``, numpy) describe the same batch for parts that plan on
+    the host; graph-safe parts read the device arrays only.
+    """
+    n_tokens: int
+    n_segments: int
+    dtype: torch.dtype
+    device: torch.device
+    token_ids: torch.Tensor          # [N]
+    positions: torch.Tensor          # [N] absolute position of each token
+    token_row: torch.Tensor          # [N] request slot (row of block tables / state slots)
+    seg_row: torch.Tensor            # [S] request slot of each segment
+    seg_start: torch.Tensor          # [S] first token of the segment in the flat batch
+    seg_len: torch.Tensor            # [S]
+    seg_pos0: torch.Tensor           # [S] position of the segment's first token
+    # query tiles of segments longer than one token: (segment, offset inside it)
+    n_tiles: int
+    tile_seg: torch.Tensor           # [n_tiles]
+    tile_off: torch.Tensor           # [n_tiles]
+    # segments of exactly one token (decode rows)
+    n_decode: int
+    decode_seg: torch.Tensor         # [n_decode]
+    max_context: int                 # largest start+len over the batch's segments (host upper bound)
+    h_seg_row: object = None
+    h_seg_start: object = None
+    h_seg_len: object = None
+    h_seg_pos0: object = None
+    extras: dict = field(default_factory=dict)
+
+    def empty(self, shape, dtype=None):
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

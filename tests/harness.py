@@ -1,0 +1,175 @@
+"""Shared helpers of the GPU tests: tiny model folders, replay schedules, comparisons."""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import torch
+
+from qwen_inference_lab_b200.weights import write_safetensors
+from tests.plain import qwen3_plain as plain
+from tests.tiny_configs import tiny_weights
+
+TOLERANCE = {torch.float32: dict(atol=1e-5, rtol=1e-5), torch.bfloat16: dict(atol=4e-3, rtol=2e-2)}
+
+
+def write_folder(cfg, seed, folder, storage=torch.bfloat16) -> dict:
+    """Write config.json + model.safetensors for a tiny configuration; returns the float32 weights."""
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    weights = tiny_weights(cfg, seed, torch.float32)
+    stored = {k: v.to(storage) for k, v in weights.items()}
+    if cfg.get("tie_word_embeddings", True):
+        stored.pop("lm_head.weight", None)
+    (folder / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(folder / "model.safetensors", stored)
+    return weights
+
+
+def random_tokens(cfg, count, seed):
+    generator = torch.Generator().manual_seed(seed)
+    return torch.randint(0, cfg["vocab_size"], (count,), generator=generator).tolist()
+
+
+def build_engine_parts(folder, dtype, *, num_pages, page_size, max_requests=4, use_graphs=True):
+    from qwen_inference_lab_b200.cache import CacheManager
+    from qwen_inference_lab_b200.engine import StepRunner
+    from qwen_inference_lab_b200.loading import load_model
+    model = load_model(folder, device="cuda", dtype=dtype)
+    cache = CacheManager(model.cache_specs(), num_pages=num_pages, page_size=page_size,
+                         max_requests=max_requests, max_context=model.max_positions, dtype=dtype,
+                         device=model.device)
+    cache.poison()
+    runner = StepRunner(model, cache, max_step_tokens=1024, use_graphs=use_graphs)
+    return model, cache, runner
+
+
+def run_schedule(runner, cache, schedule):
+    """schedule: list of steps; a step is (entries, ended) with entries = [(id, tokens, want)].
+
+    Returns {(id, absolute position): float32 logits row on the CPU}.
+    """
+    from qwen_inference_lab_b200.engine import StepEntry
+    rows = {}
+    for entries, ended in schedule:
+        batch = []
+        for request_id, tokens, want in entries:
+            if request_id not in cache.rows:
+                assert cache.admit(request_id)
+            batch.append(StepEntry(request_id, list(tokens), list(want)))
+        starts = {e.request_id: cache.written(e.request_id) for e in batch}
+        logits = runner.run(batch) if batch else None
+        if logits is not None:
+            logits = logits.float().cpu()
+            index = 0
+            for e in batch:
+                for w in e.want:
+                    rows[(e.request_id, starts[e.request_id] + w)] = logits[index]
+                    index += 1
+            assert index == logits.shape[0]
+        for request_id in ended:
+            cache.release(request_id)
+        cache.check_invariants()
+    return rows
+
+
+def cut(tokens, sizes):
+    """Cut ``tokens`` into portions of the given sizes, repeating the pattern as needed."""
+    portions, i, k = [], 0, 0
+    while i < len(tokens):
+        size = sizes[k % len(sizes)]
+        portions.append(tokens[i:i + size])
+        i += size
+        k += 1
+    return portions
+
+
+def whole_schedule(requests):
+    """Each request alone and whole, all positions wanted."""
+    return [([(rid, tokens, list(range(len(tokens))))], [rid]) for rid, tokens in requests.items()]
+
+
+def tail_decode_schedule(requests, tail=32):
+    """Most of a request in one step, its last ``tail`` tokens one by one."""
+    schedule = []
+    for rid, tokens in requests.items():
+        head = max(1, len(tokens) - tail)
+        schedule.append(([(rid, tokens[:head], list(range(head)))], []))
+        for i in range(head, len(tokens)):
+            schedule.append(([(rid, tokens[i:i + 1], [0])], [rid] if i == len(tokens) - 1 else []))
+        if head == len(tokens):
+            schedule[-1] = (schedule[-1][0], [rid])
+    return schedule
+
+
+def chunk_schedule(requests, sizes=(16, 7, 2, 5, 2, 33, 3)):
+    schedule = []
+    for rid, tokens in requests.items():
+        portions = cut(tokens, sizes)
+        for i, portion in enumerate(portions):
+            schedule.append(([(rid, portion, list(range(len(portion))))], [rid] if i == len(portions) - 1 else []))
+    return schedule
+
+
+def mixed_schedule(requests, max_live=4, sizes=(9, 2, 17, 4, 30)):
+    """Up to ``max_live`` requests at once: portions of prompts beside single tokens of others.
+
+    Every request first walks through the first 60% of its tokens in portions, then the
+    rest one token a step; a request is left out of a step now and then; a new one starts
+    when one ends, so pages are given back and used again.
+    """
+    pending = list(requests.items())
+    live, schedule, tick = {}, [], 0
+    while pending or live:
+        while pending and len(live) < max_live:
+            rid, tokens = pending.pop(0)
+            live[rid] = dict(tokens=tokens, done=0, split=max(2, int(len(tokens) * 0.6)), k=len(live))
+        entries, ended = [], []
+        for rid, state in list(live.items()):
+            tick += 1
+            if tick % 5 == 0 and len(live) > 1:
+                continue        # sits this step out
+            remaining = len(state["tokens"]) - state["done"]
+            if state["done"] < state["split"]:
+                size = min(sizes[(state["k"] + tick) % len(sizes)], state["split"] - state["done"])
+            else:
+                size = 1
+            size = min(size, remaining)
+            portion = state["tokens"][state["done"]:state["done"] + size]
+            entries.append((rid, portion, list(range(len(portion)))))
+            state["done"] += size
+            if state["done"] == len(state["tokens"]):
+                ended.append(rid)
+                del live[rid]
+        if entries:
+            schedule.append((entries, ended))
+    return schedule
+
+
+def plain_rows(requests, weights, cfg, dtype=torch.float32):
+    rows = {}
+    for rid, tokens in requests.items():
+        logits = plain.logits(tokens, weights, cfg, dtype)
+        for position in range(len(tokens)):
+            rows[(rid, position)] = logits[position]
+    return rows
+
+
+def assert_rows_close(actual, expected, dtype, what=""):
+    assert set(actual) == set(expected), f"{what}: different (request, position) sets"
+    tolerance = TOLERANCE[dtype]
+    worst, worst_key = 0.0, None
+    for key in sorted(expected, key=lambda k: (str(k[0]), k[1])):
+        a, e = actual[key], expected[key]
+        assert torch.isfinite(a).all(), f"{what}: non-finite logits at {key}"
+        excess = ((a - e).abs() - tolerance["atol"] - tolerance["rtol"] * e.abs()).max().item()
+        if excess > worst:
+            worst, worst_key = excess, key
+    if worst_key is not None:
+        a, e = actual[worst_key], expected[worst_key]
+        first = min((k for k in expected if ((actual[k] - expected[k]).abs() - tolerance["atol"]
+                                             - tolerance["rtol"] * expected[k].abs()).max() > 0),
+                    key=lambda k: (str(k[0]), k[1]))
+        raise AssertionError(
+            f"{what}: logits differ; first wrong (request, position) = {first}, worst = {worst_key} "
+            f"max abs difference {(a - e).abs().max().item():.3e}")

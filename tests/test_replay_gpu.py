@@ -1,0 +1,49 @@
+"""Replay of the same requests under four ways of cutting the work, against the plain implementation."""
+import pytest
+import torch
+
+from tests import harness
+from tests.tiny_configs import TINY_A, TINY_B, TINY_C
+
+pytestmark = pytest.mark.gpu
+
+CASES = {
+    "A": dict(cfg=TINY_A, seed=0, page_size=4, lengths=(5, 17, 33, 90)),
+    "B": dict(cfg=TINY_B, seed=1, page_size=8, lengths=(1, 9, 31, 64, 100, 150)),
+    "C": dict(cfg=TINY_C, seed=2, page_size=16, lengths=(40, 3, 130, 70)),
+}
+SCHEDULES = {
+    "whole": harness.whole_schedule,
+    "tail_decode": harness.tail_decode_schedule,
+    "chunks": harness.chunk_schedule,
+    "mixed": harness.mixed_schedule,
+}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    result = {}
+    for name, case in CASES.items():
+        folder = tmp_path_factory.mktemp(f"tiny{name}")
+        weights = harness.write_folder(case["cfg"], case["seed"], folder)
+        requests = {f"r{i}": harness.random_tokens(case["cfg"], n, 50 + i) for i, n in enumerate(case["lengths"])}
+        result[name] = (folder, weights, requests)
+    return result
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+@pytest.mark.parametrize("schedule", list(SCHEDULES))
+@pytest.mark.parametrize("case", list(CASES))
+def test_replay_matches_plain(folders, case, schedule, dtype):
+    folder, weights, requests = folders[case]
+    cfg, page_size = CASES[case]["cfg"], CASES[case]["page_size"]
+    longest = max(len(t) for t in requests.values())
+    # so few pages that a mixed run must reuse the pages of finished requests
+    live = 4 if schedule == "mixed" else 1
+    num_pages = live * ((longest + page_size - 1) // page_size) if schedule == "mixed" \
+        else (longest + page_size - 1) // page_size
+    _, cache, runner = harness.build_engine_parts(folder, dtype, num_pages=num_pages, page_size=page_size)
+    actual = harness.run_schedule(runner, cache, SCHEDULES[schedule](requests))
+    assert cache.free_pages() == num_pages and not cache.owners()
+    expected = harness.plain_rows(requests, weights, cfg, dtype)
+    harness.assert_rows_close(actual, expected, dtype, f"tiny {case} {schedule} {dtype}")
