@@ -1,0 +1,512 @@
+// bfloat16 causal grouped-query attention over the paged cache on the tensor
+// cores (mma.sync m16n8k16, float32 accumulation, float32 softmax), compiled for
+// one head size: -DQIL_HEAD_DIM=<multiple of 16, at most 256>.
+//
+// Two forms, one arithmetic (scores = q k^T * head_dim^-1/2 over keys j <= the
+// token's absolute position and inside the window; softmax; times v;
+// qil/model.py:59-68, qil/paged_attention.py:25-41):
+//
+//  * portions of prompts: one block per (tile of 64 query tokens of a segment,
+//    query head).  Keys and values of the segment's request stream through
+//    shared memory in tiles of 64 positions, found through the block table, with
+//    an online softmax; history written by earlier steps and the portion's own
+//    keys are treated alike.
+//  * single tokens: one block per (span of 256 positions, kv head, token) serves
+//    all query heads of that kv head at once, so every key byte is read once;
+//    blocks write unnormalised partial sums and (max, sum) to scratch memory and
+//    a second kernel merges the spans in ascending order
+//    (the reference's partition + merge kernels, qil/paged_attention.py:13-58).
+//
+// Key tiles and spans are aligned to absolute positions, so a token's result
+// does not depend on the batch it is in.
+// Cache layout of one layer: [page][2 (K,V)][kv_head][slot in page][head_dim].
+#include "common.cuh"
+
+#ifndef QIL_HEAD_DIM
+#error "compile with -DQIL_HEAD_DIM=<head size>"
+#endif
+static_assert(QIL_HEAD_DIM % 16 == 0 && QIL_HEAD_DIM >= 16 && QIL_HEAD_DIM <= 256,
+              "the tensor-core attention takes head sizes 16, 32, ..., 256");
+
+QIL_ERROR_STORAGE
+
+#define KV_TILE 64          // key positions per shared-memory tile
+#define Q_TILE 64           // query tokens per block (prompt portions)
+#define DECODE_SPAN 256     // key positions per block (single tokens)
+
+constexpr int D = QIL_HEAD_DIM;
+constexpr int LDS = D + 8;           // shared-memory row stride in elements: rows start 16 bytes apart mod 128
+constexpr int KSTEPS = D / 16;
+constexpr bool Q_IN_REGS = (D <= 128);
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct AttnParams {
+    const bf16* q;            // [N, Hq, D]
+    const bf16* kv;           // one layer's pages
+    bf16* out;                // [N, Hq, D]
+    const int* seg_start;
+    const int* seg_len;
+    const int* seg_pos0;
+    const int* seg_row;
+    const int* block_table;
+    int table_stride;
+    int n_q_heads, n_kv_heads, page_size, num_pages, window;
+    float scale_log2;         // head_dim^-1/2 * log2(e)
+};
+
+// Load 64 key rows and 64 value rows (positions tile*64 ...) of one kv head into shared memory.
+// Two threads per row; rows outside [lo, hi] or without a page are zero-filled.
+__device__ __forceinline__ void load_kv_tile(const AttnParams& p, const int* table, int kv_head, int tile,
+                                             int lo, int hi, bf16* sK, bf16* sV, int tid) {
+    const int row = tid >> 1, half = tid & 1;
+    const int pos = tile * KV_TILE + row;
+    bool valid = pos >= lo && pos <= hi;
+    size_t offset = 0;
+    if (valid) {
+        const int page = table[pos / p.page_size];
+        valid = page >= 0 && page < p.num_pages;
+        if (valid)
+            offset = ((((size_t)page * 2) * p.n_kv_heads + kv_head) * p.page_size + (pos % p.page_size)) * D;
+    }
+    const bf16* k_src = p.kv + offset;
+    const bf16* v_src = k_src + (size_t)p.n_kv_heads * p.page_size * D;
+    constexpr int CHUNKS = D / 16;   // 16-byte chunks per thread per row
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int col = (half * CHUNKS + c) * 8;
+        cp_async16(sK + row * LDS + col, k_src + col, valid);
+        cp_async16(sV + row * LDS + col, v_src + col, valid);
+    }
+}
+
+// ------------------------------------------------------------------ prompt portions
+__global__ void __launch_bounds__(128)
+attn_prefill_kernel(AttnParams p, const int* __restrict__ tile_seg, const int* __restrict__ tile_off) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [64][LDS]
+    bf16* sK = sQ + Q_TILE * LDS;                       // [2][64][LDS]
+    bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int head = blockIdx.y;
+    const int kv_head = head / (p.n_q_heads / p.n_kv_heads);
+    const int seg = tile_seg[blockIdx.x], off = tile_off[blockIdx.x];
+    const int rows = min(Q_TILE, p.seg_len[seg] - off);
+    const int n0 = p.seg_start[seg] + off;
+    const int pos0 = p.seg_pos0[seg] + off;
+    const int hi = pos0 + rows - 1;
+    const int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+    const int* table = p.block_table + (size_t)p.seg_row[seg] * p.table_stride;
+
+    {   // queries of this tile: two threads per row
+        const int row = tid >> 1, half = tid & 1;
+        const bool valid = row < rows;
+        const bf16* src = p.q + ((size_t)(n0 + (valid ? row : 0)) * p.n_q_heads + head) * D;
+        constexpr int CHUNKS = D / 16;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int col = (half * CHUNKS + c) * 8;
+            cp_async16(sQ + row * LDS + col, src + col, valid);
+        }
+    }
+    const int first_tile = lo / KV_TILE, last_tile = hi / KV_TILE;
+    load_kv_tile(p, table, kv_head, first_tile, lo, hi, sK, sV, tid);
+    cp_async_commit();
+
+    unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
+    const int pos_a = pos0 + row_a, pos_b = pos0 + row_b;
+
+    for (int tile = first_tile; tile <= last_tile; ++tile) {
+        const int buf = (tile - first_tile) & 1;
+        if (tile + 1 <= last_tile)
+            load_kv_tile(p, table, kv_head, tile + 1, lo, hi, sK + (buf ^ 1) * KV_TILE * LDS,
+                         sV + (buf ^ 1) * KV_TILE * LDS, tid);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (Q_IN_REGS && tile == first_tile) {
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks)
+                ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+                            sQ + (warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + ks * 16 + (lane >> 4) * 8);
+        }
+        const bf16* tK = sK + buf * KV_TILE * LDS;
+        const bf16* tV = sV + buf * KV_TILE * LDS;
+
+        float s[KV_TILE / 8][4];
+#pragma unroll
+        for (int i = 0; i < KV_TILE / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            unsigned a[4];
+            if (Q_IN_REGS) {
+                a[0] = qf[ks][0]; a[1] = qf[ks][1]; a[2] = qf[ks][2]; a[3] = qf[ks][3];
+            } else {
+                ldmatrix_x4(a[0], a[1], a[2], a[3],
+                            sQ + (warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + ks * 16 + (lane >> 4) * 8);
+            }
+#pragma unroll
+            for (int np = 0; np < KV_TILE / 16; ++np) {
+                unsigned b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3,
+                            tK + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16(s[2 * np], a, b0, b1);
+                mma_bf16(s[2 * np + 1], a, b2, b3);
+            }
+        }
+        // scale, mask by absolute position, online softmax (float32)
+        float tmax_a = -INFINITY, tmax_b = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < KV_TILE / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = tile * KV_TILE + nt * 8 + (lane & 3) * 2 + (e & 1);
+                const int pos = (e < 2) ? pos_a : pos_b;
+                const bool ok = key <= pos && (p.window == 0 || key > pos - p.window);
+                const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
+            }
+        }
+        tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 1));
+        tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 2));
+        tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 1));
+        tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 2));
+        const float mn_a = fmaxf(m_a, tmax_a), mn_b = fmaxf(m_b, tmax_b);
+        const float ms_a = (mn_a == -INFINITY) ? 0.f : mn_a, ms_b = (mn_b == -INFINITY) ? 0.f : mn_b;
+        const float corr_a = exp2f(m_a - ms_a), corr_b = exp2f(m_b - ms_b);
+        m_a = mn_a; m_b = mn_b;
+        float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < KV_TILE / 8; ++nt) {
+            s[nt][0] = exp2f(s[nt][0] - ms_a); s[nt][1] = exp2f(s[nt][1] - ms_a);
+            s[nt][2] = exp2f(s[nt][2] - ms_b); s[nt][3] = exp2f(s[nt][3] - ms_b);
+            sum_a += s[nt][0] + s[nt][1];
+            sum_b += s[nt][2] + s[nt][3];
+        }
+        l_a = l_a * corr_a + sum_a;
+        l_b = l_b * corr_b + sum_b;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+#pragma unroll
+        for (int kt = 0; kt < KV_TILE / 16; ++kt) {
+            unsigned a[4];
+            a[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+            a[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+            a[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+            a[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < D / 16; ++dp) {
+                unsigned b0, b1, b2, b3;
+                ldmatrix_x4_trans(b0, b1, b2, b3,
+                                  tV + (kt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + dp * 16 + (lane >> 4) * 8);
+                mma_bf16(o[2 * dp], a, b0, b1);
+                mma_bf16(o[2 * dp + 1], a, b2, b3);
+            }
+        }
+        __syncthreads();   // everyone is done with this buffer before the next prefetch overwrites it
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+        const int col = dt * 8 + (lane & 3) * 2;
+        if (row_a < rows)
+            *reinterpret_cast<unsigned*>(p.out + ((size_t)(n0 + row_a) * p.n_q_heads + head) * D + col) =
+                pack_bf16(o[dt][0] * inv_a, o[dt][1] * inv_a);
+        if (row_b < rows)
+            *reinterpret_cast<unsigned*>(p.out + ((size_t)(n0 + row_b) * p.n_q_heads + head) * D + col) =
+                pack_bf16(o[dt][2] * inv_b, o[dt][3] * inv_b);
+    }
+}
+
+// ------------------------------------------------------------------ single tokens: spans
+// part_o  [n_decode, Hq, n_spans, D] float32, unnormalised; part_ml [n_decode, Hq, n_spans, 2] (max, sum).
+__global__ void __launch_bounds__(128)
+attn_decode_span_kernel(AttnParams p, const int* __restrict__ decode_seg, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int n_spans) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [16][LDS]
+    bf16* sK = sQ + 16 * LDS;                           // [2][64][LDS]
+    bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int group = p.n_q_heads / p.n_kv_heads;
+    const int chunks = (group + 15) / 16;
+    const int kv_head = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * 16;
+    const int gcount = min(16, group - g0);
+    const int span = blockIdx.x, d_idx = blockIdx.z;
+    const int seg = decode_seg[d_idx];
+    const int n = p.seg_start[seg], pos = p.seg_pos0[seg];
+    const int hi = pos;
+    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int k_begin = span * DECODE_SPAN;
+    if (k_begin > hi || k_begin + DECODE_SPAN <= lo) return;    // the merge skips the same spans
+    const int* table = p.block_table + (size_t)p.seg_row[seg] * p.table_stride;
+    const int first_tile = max(k_begin, lo) / KV_TILE;
+    const int last_tile = min(k_begin + DECODE_SPAN - 1, hi) / KV_TILE;
+
+    {   // the query heads of this kv head: 8 threads per row
+        const int row = tid >> 3;
+        const bool valid = row < gcount;
+        const bf16* src = p.q + ((size_t)n * p.n_q_heads + kv_head * group + g0 + (valid ? row : 0)) * D;
+        for (int c = tid & 7; c < D / 8; c += 8) cp_async16(sQ + row * LDS + c * 8, src + c * 8, valid);
+    }
+    load_kv_tile(p, table, kv_head, first_tile, lo, hi, sK, sV, tid);
+    cp_async_commit();
+
+    unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+    for (int tile = first_tile; tile <= last_tile; ++tile) {
+        const int buf = (tile - first_tile) & 1;
+        if (tile + 1 <= last_tile)
+            load_kv_tile(p, table, kv_head, tile + 1, lo, hi, sK + (buf ^ 1) * KV_TILE * LDS,
+                         sV + (buf ^ 1) * KV_TILE * LDS, tid);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (Q_IN_REGS && tile == first_tile) {
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks)
+                ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+                            sQ + (((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + ks * 16 + (lane >> 4) * 8);
+        }
+        const bf16* tK = sK + buf * KV_TILE * LDS + warp * 16 * LDS;   // this warp's 16 keys of the tile
+        const bf16* tV = sV + buf * KV_TILE * LDS + warp * 16 * LDS;
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
+        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            unsigned a[4];
+            if (Q_IN_REGS) {
+                a[0] = qf[ks][0]; a[1] = qf[ks][1]; a[2] = qf[ks][2]; a[3] = qf[ks][3];
+            } else {
+                ldmatrix_x4(a[0], a[1], a[2], a[3],
+                            sQ + (((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + ks * 16 + (lane >> 4) * 8);
+            }
+            unsigned b0, b1, b2, b3;
+            ldmatrix_x4(b0, b1, b2, b3, tK + ((lane >> 4) * 8 + (lane & 7)) * LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[0], a, b0, b1);
+            mma_bf16(s[1], a, b2, b3);
+        }
+        float tmax = -INFINITY;     // every row is the same position: one mask for all
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = tile * KV_TILE + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                const bool ok = key <= hi && key >= lo;
+                s[nt][e] = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
+            }
+        }
+        float tmax_a = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        float tmax_b = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        (void)tmax;
+        tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 1));
+        tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 2));
+        tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 1));
+        tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 2));
+        const float mn_a = fmaxf(m_a, tmax_a), mn_b = fmaxf(m_b, tmax_b);
+        const float ms_a = (mn_a == -INFINITY) ? 0.f : mn_a, ms_b = (mn_b == -INFINITY) ? 0.f : mn_b;
+        const float corr_a = exp2f(m_a - ms_a), corr_b = exp2f(m_b - ms_b);
+        m_a = mn_a; m_b = mn_b;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            s[nt][0] = exp2f(s[nt][0] - ms_a); s[nt][1] = exp2f(s[nt][1] - ms_a);
+            s[nt][2] = exp2f(s[nt][2] - ms_b); s[nt][3] = exp2f(s[nt][3] - ms_b);
+        }
+        l_a = l_a * corr_a + (s[0][0] + s[0][1] + s[1][0] + s[1][1]);
+        l_b = l_b * corr_b + (s[0][2] + s[0][3] + s[1][2] + s[1][3]);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+        unsigned a[4];
+        a[0] = pack_bf16(s[0][0], s[0][1]);
+        a[1] = pack_bf16(s[0][2], s[0][3]);
+        a[2] = pack_bf16(s[1][0], s[1][1]);
+        a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int dp = 0; dp < D / 16; ++dp) {
+            unsigned b0, b1, b2, b3;
+            ldmatrix_x4_trans(b0, b1, b2, b3, tV + (((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + dp * 16 + (lane >> 4) * 8);
+            mma_bf16(o[2 * dp], a, b0, b1);
+            mma_bf16(o[2 * dp + 1], a, b2, b3);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+    // merge the four warps' (max, sum, acc) through shared memory (the tile buffers are free now)
+    float* wm = reinterpret_cast<float*>(sK);          // [4][16]
+    float* wl = wm + 4 * 16;                            // [4][16]
+    float* wo = wl + 4 * 16;                            // [4][16][D]
+    const int ra = lane >> 2, rb = ra + 8;
+    if ((lane & 3) == 0) {
+        wm[warp * 16 + ra] = m_a; wm[warp * 16 + rb] = m_b;
+        wl[warp * 16 + ra] = l_a; wl[warp * 16 + rb] = l_b;
+    }
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+        const int col = dt * 8 + (lane & 3) * 2;
+        wo[(warp * 16 + ra) * D + col] = o[dt][0]; wo[(warp * 16 + ra) * D + col + 1] = o[dt][1];
+        wo[(warp * 16 + rb) * D + col] = o[dt][2]; wo[(warp * 16 + rb) * D + col + 1] = o[dt][3];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < gcount * D; idx += 128) {
+        const int r = idx / D, col = idx - r * D;
+        float mx = fmaxf(fmaxf(wm[r], wm[16 + r]), fmaxf(wm[32 + r], wm[48 + r]));
+        const float ms = (mx == -INFINITY) ? 0.f : mx;
+        float acc = 0.f, sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = exp2f(wm[w * 16 + r] - ms);
+            acc += f * wo[(w * 16 + r) * D + col];
+            sum += f * wl[w * 16 + r];
+        }
+        const int head = kv_head * group + g0 + r;
+        const size_t slot = ((size_t)d_idx * p.n_q_heads + head) * n_spans + span;
+        part_o[slot * D + col] = acc;
+        if (col == 0) { part_ml[slot * 2] = mx; part_ml[slot * 2 + 1] = sum; }
+    }
+}
+
+// ------------------------------------------------------------------ single tokens: merge of the spans
+__global__ void __launch_bounds__(128)
+attn_decode_merge_kernel(AttnParams p, const int* __restrict__ decode_seg, const float* __restrict__ part_o,
+                         const float* __restrict__ part_ml, int n_spans) {
+    const int head = blockIdx.x, d_idx = blockIdx.y;
+    const int seg = decode_seg[d_idx];
+    const int n = p.seg_start[seg], pos = p.seg_pos0[seg];
+    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int s_lo = lo / DECODE_SPAN;
+    int s_hi = pos / DECODE_SPAN;
+    if (s_hi >= n_spans) s_hi = n_spans - 1;   // cannot happen when the host sized n_spans for the batch
+    const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
+    float mx = -INFINITY;
+    for (int s = s_lo; s <= s_hi; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
+    const float ms = (mx == -INFINITY) ? 0.f : mx;
+    float sum = 0.f;
+    for (int s = s_lo; s <= s_hi; ++s) sum += exp2f(part_ml[(base + s) * 2] - ms) * part_ml[(base + s) * 2 + 1];
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    for (int col = threadIdx.x; col < D; col += 128) {
+        float acc = 0.f;
+        for (int s = s_lo; s <= s_hi; ++s)
+            acc += exp2f(part_ml[(base + s) * 2] - ms) * part_o[(base + s) * D + col];
+        p.out[((size_t)n * p.n_q_heads + head) * D + col] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+// ------------------------------------------------------------------ entry points
+static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, const int* seg_start,
+                       const int* seg_len, const int* seg_pos0, const int* seg_row, const int* block_table,
+                       int table_stride, int n_q_heads, int n_kv_heads, int page_size, int num_pages,
+                       int window, float scale) {
+    if (n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads)
+        QIL_REFUSE("attention: %d query heads do not divide into %d kv heads", n_q_heads, n_kv_heads);
+    if (page_size <= 0 || num_pages <= 0 || window < 0 || table_stride <= 0)
+        QIL_REFUSE("attention: page_size %d pages %d window %d table width %d", page_size, num_pages, window, table_stride);
+    if (((uintptr_t)q | (uintptr_t)kv | (uintptr_t)out) & 15)
+        QIL_REFUSE("attention: q, cache and out must be 16-byte aligned");
+    p.q = (const bf16*)q; p.kv = (const bf16*)kv; p.out = (bf16*)out;
+    p.seg_start = seg_start; p.seg_len = seg_len; p.seg_pos0 = seg_pos0; p.seg_row = seg_row;
+    p.block_table = block_table; p.table_stride = table_stride;
+    p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
+    p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    return 0;
+}
+
+extern "C" int qil_attn_head_dim() { return D; }
+extern "C" int qil_attn_decode_span() { return DECODE_SPAN; }
+
+extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const int* tile_seg, const int* tile_off,
+                                int n_tiles, const int* seg_start, const int* seg_len, const int* seg_pos0,
+                                const int* seg_row, const int* block_table, int table_stride, int n_q_heads,
+                                int n_kv_heads, int page_size, int num_pages, int window, float scale,
+                                cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    AttnParams p;
+    if (fill_params(p, q, kv, out, seg_start, seg_len, seg_pos0, seg_row, block_table, table_stride, n_q_heads,
+                    n_kv_heads, page_size, num_pages, window, scale)) return -1;
+    if (n_q_heads > 65535) QIL_REFUSE("attention: too many heads (%d)", n_q_heads);
+    const int smem = (Q_TILE + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    attn_prefill_kernel<<<dim3(n_tiles, n_q_heads), 128, smem, stream>>>(p, tile_seg, tile_off);
+    QIL_CHECK_LAUNCH();
+}
+
+// Scratch: part_o needs n_decode * Hq * n_spans * D floats, part_ml n_decode * Hq * n_spans * 2 floats.
+// n_spans must cover the longest context of the batch: ceil(max(position + 1) / DECODE_SPAN).
+extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const int* decode_seg, int n_decode,
+                               float* part_o, float* part_ml, int n_spans, const int* seg_start,
+                               const int* seg_len, const int* seg_pos0, const int* seg_row,
+                               const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                               int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
+    if (n_decode <= 0) return 0;
+    AttnParams p;
+    if (fill_params(p, q, kv, out, seg_start, seg_len, seg_pos0, seg_row, block_table, table_stride, n_q_heads,
+                    n_kv_heads, page_size, num_pages, window, scale)) return -1;
+    if (n_spans <= 0 || part_o == nullptr || part_ml == nullptr) QIL_REFUSE("attention: decode needs scratch for %d spans", n_spans);
+    const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
+    if (n_kv_heads * chunks > 65535 || n_decode > 65535) QIL_REFUSE("attention: grid too large");
+    const int tile_bytes = (16 + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
+    const int merge_bytes = 16 * LDS * (int)sizeof(bf16) + (2 * 4 * 16 + 4 * 16 * D) * (int)sizeof(float);
+    const int smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_span_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    attn_decode_span_kernel<<<dim3(n_spans, n_kv_heads * chunks, n_decode), 128, smem, stream>>>(
+        p, decode_seg, part_o, part_ml, n_spans);
+    {
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }
+    }
+    attn_decode_merge_kernel<<<dim3(n_q_heads, n_decode), 128, 0, stream>>>(p, decode_seg, part_o, part_ml, n_spans);
+    QIL_CHECK_LAUNCH();
+}

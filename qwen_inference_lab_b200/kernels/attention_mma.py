@@ -1,10 +1,83 @@
-"""Tensor-core attention kernels for bfloat16 (compiled per head size on first use)."""
+"""Tensor-core attention for bfloat16, compiled per head size on first use.
+
+``attend`` runs both forms over one step's batch: query tiles of prompt portions
+go to the tiled kernel, single tokens to the span kernel plus its merge.  The
+span kernel's partial sums live in scratch that is allocated once per step and
+shared by all layers.
+"""
 from __future__ import annotations
+
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import build
+from .ops import KernelError, _check, _p, _stream
+
+_libs: dict = {}
+DECODE_SPAN = 256
 
 
 def supports(head_dim, n_q_heads, n_kv_heads) -> bool:
-    return False
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256 and n_q_heads % n_kv_heads == 0
+
+
+def library(head_dim):
+    lib = _libs.get(head_dim)
+    if lib is None:
+        if not supports(head_dim, 1, 1):
+            raise KernelError(f"the tensor-core attention takes head sizes 16, 32, ..., 256, not {head_dim}")
+        lib = build.load(f"qil_attn_d{head_dim}", ["attention_mma.cu"], {"QIL_HEAD_DIM": head_dim})
+        if lib.qil_attn_head_dim() != head_dim or lib.qil_attn_decode_span() != DECODE_SPAN:
+            raise KernelError("attention library was built for other constants")
+        _libs[head_dim] = lib
+    return lib
+
+
+def decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim):
+    key = ("attn_decode_scratch", n_decode, n_q_heads, n_spans, head_dim)
+    scratch = ctx.extras.get(key)
+    if scratch is None:
+        slots = n_decode * n_q_heads * n_spans
+        scratch = (torch.empty(slots * head_dim, dtype=torch.float32, device=ctx.device),
+                   torch.empty(slots * 2, dtype=torch.float32, device=ctx.device))
+        ctx.extras[key] = scratch
+    return scratch
+
+
+def prefill(q, pages, out, tile_seg, tile_off, n_tiles, seg_start, seg_len, seg_pos0, seg_row, block_table,
+            n_q_heads, n_kv_heads, head_dim, page_size, window, scale):
+    lib = library(head_dim)
+    _check(lib, lib.qil_attn_prefill(
+        _p(q), _p(pages), _p(out), _p(tile_seg), _p(tile_off), c_int(n_tiles), _p(seg_start), _p(seg_len),
+        _p(seg_pos0), _p(seg_row), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads),
+        c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), _stream()),
+        "attention (prompt portions)")
+
+
+def decode(q, pages, out, decode_seg, n_decode, part_o, part_ml, n_spans, seg_start, seg_len, seg_pos0, seg_row,
+           block_table, n_q_heads, n_kv_heads, head_dim, page_size, window, scale):
+    lib = library(head_dim)
+    _check(lib, lib.qil_attn_decode(
+        _p(q), _p(pages), _p(out), _p(decode_seg), c_int(n_decode), _p(part_o), _p(part_ml), c_int(n_spans),
+        _p(seg_start), _p(seg_len), _p(seg_pos0), _p(seg_row), _p(block_table), c_int(block_table.shape[1]),
+        c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window),
+        c_float(scale), _stream()), "attention (single tokens)")
 
 
 def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
-    raise NotImplementedError
+    """q, out bfloat16 [N, Hq*D]; cache a KVCacheView whose pages already hold this step's keys and values."""
+    if q.dtype != torch.bfloat16 or cache.pages.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core attention takes bfloat16 queries and pages")
+    if tuple(cache.pages.shape[1:]) != (2, n_kv_heads, cache.page_size, head_dim):
+        raise KernelError(f"attention: cache layout {tuple(cache.pages.shape)}")
+    if ctx.n_tiles:
+        prefill(q, cache.pages, out, ctx.tile_seg, ctx.tile_off, ctx.n_tiles, ctx.seg_start, ctx.seg_len,
+                ctx.seg_pos0, ctx.seg_row, cache.block_table, n_q_heads, n_kv_heads, head_dim,
+                cache.page_size, window, scale)
+    if ctx.n_decode:
+        n_spans = max(1, (ctx.max_context + DECODE_SPAN - 1) // DECODE_SPAN)
+        part_o, part_ml = decode_scratch(ctx, ctx.n_decode, n_q_heads, n_spans, head_dim)
+        decode(q, cache.pages, out, ctx.decode_seg, ctx.n_decode, part_o, part_ml, n_spans, ctx.seg_start,
+               ctx.seg_len, ctx.seg_pos0, ctx.seg_row, cache.block_table, n_q_heads, n_kv_heads, head_dim,
+               cache.page_size, window, scale)

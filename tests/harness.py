@@ -155,21 +155,40 @@ def plain_rows(requests, weights, cfg, dtype=torch.float32):
     return rows
 
 
-def assert_rows_close(actual, expected, dtype, what=""):
+def assert_rows_close(actual, expected, dtype, what="", yardstick=None):
+    """Compare logits rows with the plain implementation's float32 rows.
+
+    float32: elementwise ``atol``/``rtol``.  bfloat16: rounding noise is as large as some
+    logits, so the bar is what bfloat16 costs the plain implementation itself: ``yardstick``
+    holds the plain implementation's rows computed in bfloat16 at the reference's rounding
+    points, and the engine may be at most 1.5 times as far from the float32 rows as that
+    (root-mean-square error of every row against the mean row error of the yardstick, and
+    the largest error against the yardstick's largest).
+    """
     assert set(actual) == set(expected), f"{what}: different (request, position) sets"
-    tolerance = TOLERANCE[dtype]
-    worst, worst_key = 0.0, None
-    for key in sorted(expected, key=lambda k: (str(k[0]), k[1])):
-        a, e = actual[key], expected[key]
-        assert torch.isfinite(a).all(), f"{what}: non-finite logits at {key}"
-        excess = ((a - e).abs() - tolerance["atol"] - tolerance["rtol"] * e.abs()).max().item()
-        if excess > worst:
-            worst, worst_key = excess, key
-    if worst_key is not None:
-        a, e = actual[worst_key], expected[worst_key]
-        first = min((k for k in expected if ((actual[k] - expected[k]).abs() - tolerance["atol"]
-                                             - tolerance["rtol"] * expected[k].abs()).max() > 0),
-                    key=lambda k: (str(k[0]), k[1]))
+    keys = sorted(expected, key=lambda k: (str(k[0]), k[1]))
+    for key in keys:
+        assert torch.isfinite(actual[key]).all(), f"{what}: non-finite logits at {key}"
+    if dtype == torch.float32:
+        tolerance = TOLERANCE[dtype]
+        bad = [k for k in keys if ((actual[k] - expected[k]).abs() - tolerance["atol"]
+                                   - tolerance["rtol"] * expected[k].abs()).max() > 0]
+        if bad:
+            worst = max(bad, key=lambda k: (actual[k] - expected[k]).abs().max().item())
+            raise AssertionError(
+                f"{what}: logits differ; first wrong (request, position) = {bad[0]}, worst = {worst} "
+                f"max abs difference {(actual[worst] - expected[worst]).abs().max().item():.3e}")
+        return
+    assert yardstick is not None, "bfloat16 comparisons need the plain bfloat16 rows as a yardstick"
+    rms = lambda rows, k: (rows[k] - expected[k]).pow(2).mean().sqrt().item()
+    peak = lambda rows, k: (rows[k] - expected[k]).abs().max().item()
+    bar_rms = 1.5 * sum(rms(yardstick, k) for k in keys) / len(keys)
+    bar_peak = 1.5 * max(peak(yardstick, k) for k in keys)
+    bad = [k for k in keys if rms(actual, k) > bar_rms * 1.5 or peak(actual, k) > bar_peak]
+    mean_rms = sum(rms(actual, k) for k in keys) / len(keys)
+    if bad or mean_rms > bar_rms:
+        worst = max(keys, key=lambda k: peak(actual, k))
         raise AssertionError(
-            f"{what}: logits differ; first wrong (request, position) = {first}, worst = {worst_key} "
-            f"max abs difference {(a - e).abs().max().item():.3e}")
+            f"{what}: bfloat16 logits are further from the float32 rows than 1.5x the plain bfloat16 "
+            f"arithmetic: first wrong (request, position) = {bad[0] if bad else None}, worst = {worst}, "
+            f"mean rms {mean_rms:.3e} (bar {bar_rms:.3e}), peak {peak(actual, worst):.3e} (bar {bar_peak:.3e})")

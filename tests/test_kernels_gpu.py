@@ -1,0 +1,313 @@
+"""Each kernel alone against a plain PyTorch float32 reference, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+IDS = ["float32", "bfloat16"]
+
+
+def ops():
+    from qwen_inference_lab_b200.kernels import ops as module
+    return module
+
+
+def close(actual, expected, dtype, scale=1.0):
+    if dtype == torch.float32:
+        torch.testing.assert_close(actual.float().cpu(), expected.float().cpu(), atol=2e-6 * scale, rtol=2e-5)
+    else:  # one bfloat16 rounding of the result (2^-8 relative) plus the same on a few inputs
+        torch.testing.assert_close(actual.float().cpu(), expected.float().cpu(), atol=8e-3 * scale, rtol=8e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("table_dtype", DTYPES, ids=IDS)
+def test_embed_gather(dtype, table_dtype):
+    torch.manual_seed(0)
+    table = torch.randn(333, 72).to(table_dtype).cuda()
+    ids = torch.tensor([0, 332, 17, 17, 5], dtype=torch.int32).cuda()
+    out = torch.empty(5, 72, dtype=dtype).cuda()
+    ops().embed_gather(table, ids, out)
+    assert torch.equal(out.cpu(), table.cpu()[ids.cpu().long()].to(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("weight_dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("width,eps", [(96, 1e-5), (1000, 1e-6), (4104, 1e-3)])
+def test_rmsnorm(dtype, weight_dtype, width, eps):
+    torch.manual_seed(1)
+    x = (torch.randn(7, width) * 3).to(dtype)
+    w = (1 + 0.1 * torch.randn(width)).to(weight_dtype)
+    expected = plain.rms_norm(x.float(), w.float(), eps) if dtype == torch.float32 else \
+        (plain.rms_norm(x, torch.ones(width), eps).float() * w.float()).to(dtype)
+    out = ops().rmsnorm(x.cuda(), w.cuda(), eps)
+    close(out, expected, dtype, scale=3)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32).cuda()
+    picked = ops().rmsnorm(x.cuda(), w.cuda(), eps, rows=rows)
+    assert torch.equal(picked.cpu(), out.cpu()[[6, 0, 3]])
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("width", [200, 37, 1024])
+def test_silu_mul(dtype, width):
+    torch.manual_seed(2)
+    gate_up = (torch.randn(9, 2 * width) * 2).to(dtype)
+    expected = torch.nn.functional.silu(gate_up[:, :width]) * gate_up[:, width:]
+    out = ops().silu_mul(gate_up.cuda())
+    close(out, expected, dtype, scale=4)
+
+
+@pytest.mark.parametrize("act,wt", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32),
+                                    (torch.float32, torch.bfloat16), (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (3, 200, 96), (65, 129, 130), (130, 64, 33)])
+def test_gemm_f32(act, wt, m, n, k):
+    torch.manual_seed(3)
+    a = torch.randn(m, k).to(act)
+    w = (torch.randn(n, k) * 0.1).to(wt)
+    bias = (torch.randn(n) * 0.1).to(wt)
+    residual = torch.randn(m, n).to(act)
+    expected = a.double() @ w.double().t() + bias.double() + residual.double()
+    out = ops().gemm_f32(a.cuda(), w.cuda(), bias=bias.cuda(), residual=residual.cuda())
+    close(out, expected.float(), act, scale=4)
+    plain_out = ops().gemm_f32(a.cuda(), w.cuda())
+    close(plain_out, (a.double() @ w.double().t()).float(), act, scale=4)
+    # a row's result does not depend on which other rows share the launch
+    alone = ops().gemm_f32(a[-1:].cuda().contiguous(), w.cuda())
+    assert torch.equal(alone.cpu()[0], plain_out.cpu()[-1])
+
+
+def paged(keys, values, page_size, num_pages, dtype, seed=0, rows=1, row=0, poison=True):
+    """Scatter dense keys/values [T, Hkv, D] into a poisoned pool through a shuffled page list."""
+    T, n_kv, d = keys.shape
+    generator = torch.Generator().manual_seed(seed)
+    order = torch.randperm(num_pages, generator=generator).tolist()
+    needed = (T + page_size - 1) // page_size
+    pool = torch.full((num_pages, 2, n_kv, page_size, d), float("nan") if poison else 0.0, dtype=dtype)
+    table = torch.full((rows, needed + 2), -1, dtype=torch.int32)
+    for i in range(needed):
+        page = order[i]
+        table[row, i] = page
+        chunk = slice(i * page_size, min(T, (i + 1) * page_size))
+        count = chunk.stop - chunk.start
+        pool[page, 0, :, :count] = keys[chunk].transpose(0, 1).to(dtype)
+        pool[page, 1, :, :count] = values[chunk].transpose(0, 1).to(dtype)
+    return pool, table
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("n_q,n_kv,d,rot,page", [(4, 2, 16, 16, 4), (6, 2, 48, 32, 3), (8, 8, 128, 128, 16), (3, 1, 72, 0, 5)])
+def test_qk_norm_rope_store(dtype, n_q, n_kv, d, rot, page):
+    from qwen_inference_lab_b200.parts import rotary_table
+    torch.manual_seed(4)
+    T, theta, eps = 11, 10000.0, 1e-5
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * d).to(dtype)
+    qw, kw = (1 + 0.1 * torch.randn(d)).to(dtype), (1 + 0.1 * torch.randn(d)).to(dtype)
+    start = 6
+    positions = torch.arange(start, start + T, dtype=torch.int32)
+    q, k, v = qkv.split([n_q * d, n_kv * d, n_kv * d], dim=1)
+    q, k, v = q.reshape(T, n_q, d), k.reshape(T, n_kv, d), v.reshape(T, n_kv, d)
+    qn, kn = plain.rms_norm(q, qw, eps), plain.rms_norm(k, kw, eps)
+    if rot:
+        angles = plain.rotary_angles(positions, rot, theta)
+        qn = torch.cat((plain.rotate(qn[..., :rot], angles), qn[..., rot:]), dim=-1)
+        kn = torch.cat((plain.rotate(kn[..., :rot], angles), kn[..., rot:]), dim=-1)
+    num_pages = 12
+    pool, table = paged(torch.zeros(start + T, n_kv, d), torch.zeros(start + T, n_kv, d), page, num_pages, dtype,
+                        rows=3, row=1)
+    pool_before = pool.clone()
+    rope = rotary_table(rot, theta, 64, dtype).cuda() if rot else None
+    q_out = torch.empty(T, n_q * d, dtype=dtype).cuda()
+    pool_gpu = pool.cuda()
+    ops().qk_norm_rope_store(qkv.cuda(), q_out, pool_gpu, qw.cuda(), kw.cuda(), eps, rope, rot, positions.cuda(),
+                             torch.full((T,), 1, dtype=torch.int32).cuda(), table.cuda(), n_q, n_kv, d, page)
+    close(q_out.reshape(T, n_q, d), qn, dtype, scale=4)
+    got = pool_gpu.cpu()
+    for i, pos in enumerate(range(start, start + T)):
+        page_id, slot = int(table[1, pos // page]), pos % page
+        close(got[page_id, 0, :, slot], kn[i], dtype, scale=4)
+        assert torch.equal(got[page_id, 1, :, slot], v[i])
+        pool_before[page_id, :, :, slot] = got[page_id, :, :, slot]
+    # nothing else in the pool was touched
+    assert torch.equal(torch.nan_to_num(got.float(), nan=-7.0), torch.nan_to_num(pool_before.float(), nan=-7.0))
+
+
+def attention_case(n_q, n_kv, d, lengths, chunk_starts, dtype, page, seed, window=0, spike=None):
+    """Requests with histories in a poisoned paged pool and query chunks over their last tokens.
+
+    Returns the flat queries, the metadata and the expected outputs of every query token.
+    ``spike`` = (request, key position): that key and the request's queries are scaled so that
+    one far score stands out, and its value is made large: a kernel that drops it shows.
+    """
+    generator = torch.Generator().manual_seed(seed)
+    num_pages = sum((n + page - 1) // page for n in lengths) + 3
+    pool = torch.full((num_pages, 2, n_kv, page, d), float("nan"), dtype=dtype)
+    free = torch.randperm(num_pages, generator=generator).tolist()
+    width = max((n + page - 1) // page for n in lengths) + 1
+    table = torch.full((len(lengths) + 1, width), -1, dtype=torch.int32)
+    q_rows, expected, seg_start, seg_len, seg_pos0, seg_row = [], [], [], [], [], []
+    for r, (length, start) in enumerate(zip(lengths, chunk_starts)):
+        keys = torch.randn(length, n_kv, d, generator=generator)
+        values = torch.randn(length, n_kv, d, generator=generator)
+        queries = torch.randn(length, n_q, d, generator=generator)
+        if spike is not None and spike[0] == r:
+            keys[spike[1]] *= 6.0
+            queries[start:] = keys[spike[1]].repeat_interleave(n_q // n_kv, dim=0)[None] * 0.8 \
+                + 0.2 * queries[start:]
+            values[spike[1]] += 25.0
+        keys, values, queries = keys.to(dtype), values.to(dtype), queries.to(dtype)
+        row = r + 1
+        for i in range((length + page - 1) // page):
+            pg = free.pop()
+            table[row, i] = pg
+            chunk = slice(i * page, min(length, (i + 1) * page))
+            pool[pg, 0, :, :chunk.stop - chunk.start] = keys[chunk].transpose(0, 1)
+            pool[pg, 1, :, :chunk.stop - chunk.start] = values[chunk].transpose(0, 1)
+        full = plain.causal_attention(queries.float(), keys.float(), values.float(), d ** -0.5, window=window)
+        seg_start.append(sum(seg_len))
+        seg_len.append(length - start)
+        seg_pos0.append(start)
+        seg_row.append(row)
+        q_rows.append(queries[start:].reshape(length - start, n_q * d))
+        expected.append(full[start:].reshape(length - start, n_q * d))
+    meta = dict(seg_start=seg_start, seg_len=seg_len, seg_pos0=seg_pos0, seg_row=seg_row)
+    return torch.cat(q_rows), pool, table, meta, torch.cat(expected)
+
+
+def flat_meta(meta):
+    positions, token_row = [], []
+    for start, length, pos0, row in zip(meta["seg_start"], meta["seg_len"], meta["seg_pos0"], meta["seg_row"]):
+        positions += list(range(pos0, pos0 + length))
+        token_row += [row] * length
+    as_int = lambda values: torch.tensor(values, dtype=torch.int32).cuda()
+    return as_int(positions), as_int(token_row)
+
+
+ATTENTION_CASES = [
+    # n_q, n_kv, d, lengths, chunk starts, page, window
+    (4, 2, 16, [1, 15, 16, 17], [0, 14, 0, 16], 4, 0),
+    (6, 2, 40, [65, 3, 511, 257], [64, 0, 300, 256], 3, 0),
+    (8, 2, 128, [1025, 1, 256, 513], [1024, 0, 200, 512], 16, 0),
+    (4, 4, 64, [31, 512], [30, 0], 8, 0),
+    (16, 1, 256, [3, 257], [2, 190], 7, 0),
+    (4, 2, 32, [300, 129, 700], [250, 128, 699], 16, 100),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("case", ATTENTION_CASES, ids=[f"case{i}" for i in range(len(ATTENTION_CASES))])
+def test_attention_generic(dtype, case):
+    n_q, n_kv, d, lengths, starts, page, window = case
+    q, pool, table, meta, expected = attention_case(n_q, n_kv, d, lengths, starts, dtype, page, seed=5, window=window)
+    positions, token_row = flat_meta(meta)
+    out = torch.empty_like(q).cuda()
+    ops().attention_generic(q.cuda(), pool.cuda(), out, positions, token_row, table.cuda(), n_q, n_kv, d, page,
+                            window, d ** -0.5)
+    close(out, expected, dtype, scale=2)
+
+
+def run_mma(q, pool, table, meta, n_q, n_kv, d, page, window):
+    from qwen_inference_lab_b200.kernels import attention_mma
+    as_int = lambda values: torch.tensor(values, dtype=torch.int32).cuda()
+    tile_seg, tile_off, decode_seg = [], [], []
+    for s, length in enumerate(meta["seg_len"]):
+        if length == 1:
+            decode_seg.append(s)
+        else:
+            for off in range(0, length, 64):
+                tile_seg.append(s)
+                tile_off.append(off)
+    out = torch.full(q.shape, float("nan"), dtype=q.dtype).cuda()
+    args = (as_int(meta["seg_start"]), as_int(meta["seg_len"]), as_int(meta["seg_pos0"]), as_int(meta["seg_row"]),
+            table.cuda())
+    qg, pg = q.cuda(), pool.cuda()
+    if tile_seg:
+        attention_mma.prefill(qg, pg, out, as_int(tile_seg), as_int(tile_off), len(tile_seg), *args,
+                              n_q, n_kv, d, page, window, d ** -0.5)
+    if decode_seg:
+        longest = max(p0 + n for p0, n in zip(meta["seg_pos0"], meta["seg_len"]))
+        n_spans = (longest + attention_mma.DECODE_SPAN - 1) // attention_mma.DECODE_SPAN + 1   # one spare span
+        part_o = torch.full((len(decode_seg) * n_q * n_spans * d,), float("nan"), dtype=torch.float32).cuda()
+        part_ml = torch.full((len(decode_seg) * n_q * n_spans * 2,), float("nan"), dtype=torch.float32).cuda()
+        attention_mma.decode(qg, pg, out, as_int(decode_seg), len(decode_seg), part_o, part_ml, n_spans, *args,
+                             n_q, n_kv, d, page, window, d ** -0.5)
+    return out
+
+
+MMA_CASES = [c for c in ATTENTION_CASES if c[2] % 16 == 0] + [
+    (32, 8, 128, [2100, 64, 640], [2099, 0, 600], 16, 0),
+    (20, 1, 48, [700, 400], [699, 330], 5, 0),          # a group of 20 heads: two head chunks per kv head
+    (6, 3, 80, [520, 130], [519, 1], 16, 64),
+]
+
+
+@pytest.mark.parametrize("case", MMA_CASES, ids=[f"case{i}" for i in range(len(MMA_CASES))])
+def test_attention_tensor_core(case):
+    n_q, n_kv, d, lengths, starts, page, window = case
+    q, pool, table, meta, expected = attention_case(n_q, n_kv, d, lengths, starts, torch.bfloat16, page, seed=6,
+                                                    window=window)
+    out = run_mma(q, pool, table, meta, n_q, n_kv, d, page, window)
+    close(out, expected, torch.bfloat16, scale=2)
+    # all-decode form of the same requests: the last token of each
+    last_q = torch.stack([q[s + n - 1] for s, n in zip(meta["seg_start"], meta["seg_len"])])
+    last_meta = dict(seg_start=list(range(len(lengths))), seg_len=[1] * len(lengths),
+                     seg_pos0=[n - 1 for n in lengths], seg_row=meta["seg_row"])
+    last_expected = torch.stack([expected[s + n - 1] for s, n in zip(meta["seg_start"], meta["seg_len"])])
+    out = run_mma(last_q, pool, table, last_meta, n_q, n_kv, d, page, window)
+    close(out, last_expected, torch.bfloat16, scale=2)
+
+
+@pytest.mark.parametrize("form", ["portion", "single"])
+def test_attention_far_key_stands_out(form):
+    """One key hundreds of positions back dominates the softmax: dropping it would change everything."""
+    n_q, n_kv, d, page = 8, 2, 64, 16
+    lengths, starts = [900, 40], ([700, 0] if form == "portion" else [899, 39])
+    q, pool, table, meta, expected = attention_case(n_q, n_kv, d, lengths, starts, torch.bfloat16, page, seed=7,
+                                                    spike=(0, 129))
+    assert expected[:lengths[0] - starts[0]].abs().mean() > 10     # the spiked value really dominates
+    out = run_mma(q, pool, table, meta, n_q, n_kv, d, page, 0)
+    close(out, expected, torch.bfloat16, scale=25)
+    generic = torch.empty_like(q).cuda()
+    positions, token_row = flat_meta(meta)
+    ops().attention_generic(q.cuda(), pool.cuda(), generic, positions, token_row, table.cuda(), n_q, n_kv, d, page,
+                            0, d ** -0.5)
+    close(generic, expected, torch.bfloat16, scale=25)
+
+
+def test_sample_rows_greedy_ties_and_nonfinite():
+    logits = torch.zeros(4, 1000)
+    logits[0, 17] = 3.0; logits[0, 900] = 3.0          # tie: lowest index wins
+    logits[1, 999] = 1.0
+    logits[2, 5] = float("nan")
+    logits[3, 7] = float("inf")
+    tokens, bad = ops().sample_rows(logits.cuda())
+    assert tokens.cpu().tolist()[:2] == [17, 999]
+    assert bad.cpu().tolist() == [0, 0, 1, 1]
+
+
+def test_sample_rows_temperature_matches_plain_and_is_batch_independent():
+    torch.manual_seed(8)
+    vocab = 1517
+    logits = torch.randn(5, vocab) * 2
+    temperature = torch.tensor([0.8, 0.0, 1.3, 0.8, 0.5])
+    seed = torch.tensor([11, 12, 13, 11, 99], dtype=torch.int64)
+    counter = torch.tensor([0, 1, 2, 0, 7], dtype=torch.int64)
+    tokens, bad = ops().sample_rows(logits.cuda(), temperature.cuda(), seed.cuda(), counter.cuda())
+    tokens = tokens.cpu().tolist()
+    assert bad.cpu().sum() == 0
+    for r in range(5):
+        assert tokens[r] == plain.sample(logits[r], float(temperature[r]), int(seed[r]), int(counter[r]))
+    alone, _ = ops().sample_rows(logits[2:3].cuda().contiguous(), temperature[2:3].cuda(), seed[2:3].cuda(),
+                                 counter[2:3].cuda())
+    assert alone.cpu().tolist() == [tokens[2]]
+    # the draws follow softmax(logits / T): chi-square-free sanity check on a small vocabulary
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).repeat(4000, 1)
+    t = torch.full((4000,), 0.7)
+    drawn, _ = ops().sample_rows(small.cuda(), t.cuda(), torch.arange(4000, dtype=torch.int64).cuda(),
+                                 torch.zeros(4000, dtype=torch.int64).cuda())
+    freq = torch.bincount(drawn.cpu().long(), minlength=4).float() / 4000
+    want = torch.softmax(small[0] / 0.7, dim=0)
+    assert (freq - want).abs().max() < 0.03
