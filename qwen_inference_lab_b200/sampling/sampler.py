@@ -1,0 +1,50 @@
+"""Choosing next tokens from the step's logits.
+
+Greedy: the largest logit, lowest index among equals; non-finite logits are an
+error, not a token (qil/engine.py:96-100).  Temperature: a draw from
+``softmax(logits / temperature)`` by the Gumbel-max rule with noise that depends
+only on (the request's seed, the index of the token being drawn, the vocabulary
+index), so that a request's tokens do not change with the batch it shares.
+The reference samples greedily only.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+
+
+class NonFiniteLogits(RuntimeError):
+    pass
+
+
+class Sampler:
+    def __init__(self, device, max_rows=256):
+        self.device = torch.device(device)
+        self._result = torch.zeros((2, max_rows), dtype=torch.int32, device=self.device)
+        self._host = torch.zeros((2, max_rows), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+
+    def _reserve(self, rows):
+        if rows > self._result.shape[1]:
+            self._result = torch.zeros((2, rows), dtype=torch.int32, device=self.device)
+            self._host = torch.zeros((2, rows), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+
+    def choose(self, logits, temperatures=None, seeds=None, counters=None) -> list:
+        """One token id per row of float32 ``logits`` [R, V]; waits for the result.
+
+        ``temperatures`` (0 = greedy), ``seeds`` and ``counters`` are host sequences of
+        length R, or None for an all-greedy batch.
+        """
+        rows = logits.shape[0]
+        self._reserve(rows)
+        t = s = c = None
+        if temperatures is not None and any(v > 0 for v in temperatures):
+            t = torch.tensor(list(temperatures), dtype=torch.float32).to(self.device, non_blocking=True)
+            s = torch.tensor([v & 0x7FFFFFFFFFFFFFFF for v in seeds], dtype=torch.int64).to(self.device, non_blocking=True)
+            c = torch.tensor(list(counters), dtype=torch.int64).to(self.device, non_blocking=True)
+        ops.sample_rows(logits, t, s, c, tokens=self._result[0, :rows], nonfinite=self._result[1, :rows])
+        self._host[:, :rows].copy_(self._result[:, :rows], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        if int(self._host[1, :rows].max()) != 0:
+            raise NonFiniteLogits("model returned non-finite logits")
+        return self._host[0, :rows].tolist()
