@@ -19,6 +19,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+from ..kernels import ops
 from ..parts.base import StepContext
 from ..utils.staging import PinnedRing
 
@@ -54,7 +55,9 @@ class StepRunner:
         self._graph_pool = None
         self._reserve(8 * max_step_tokens + 8 * cache.max_requests + 64)
         self.steps_run = 0
-        self.kernel_launch_estimate = 0
+        self.kernel_launches = 0          # this engine's own kernels (library products are not counted)
+        self.launches_per_graph: dict = {}
+        self.last_upload_bytes = 0
 
     def _reserve(self, ints):
         if ints <= self._capacity:
@@ -138,6 +141,7 @@ class StepRunner:
         if self.device.type != "cuda":
             self._meta_dev[:len(packed)] = torch.from_numpy(packed)
             return
+        self.last_upload_bytes = packed.nbytes
         stage = self._ring.acquire(packed.nbytes).view(torch.int32)[:len(packed)]
         stage.numpy()[:] = packed
         self._meta_dev[:len(packed)].copy_(stage, non_blocking=True)
@@ -165,7 +169,9 @@ class StepRunner:
         else:
             ctx = self._context(offsets, host, n, s, max_context)
             begin, count = offsets["logit_rows"]
+            before = ops.launch_count()
             logits = self.model.forward(ctx, self.views, self._meta_dev[begin:begin + count] if count else None)
+            self.kernel_launches += ops.launch_count() - before
         for entry in entries:
             self.cache.advance(entry.request_id, self.cache.written(entry.request_id) + len(entry.tokens))
         self.steps_run += 1
@@ -187,10 +193,13 @@ class StepRunner:
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
+            before = ops.launch_count()
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 logits = self.model.forward(ctx, self.views, logit_rows)
-            record = (graph, logits)
+            record = (graph, logits, ops.launch_count() - before)
             self._graphs[key] = record
-        graph, logits = record
+            self.launches_per_graph[n] = record[2]
+        graph, logits, launches = record
         graph.replay()
+        self.kernel_launches += launches
         return logits

@@ -62,7 +62,7 @@ def decode(q, pages, out, decode_seg, n_decode, part_o, part_ml, n_spans, seg_st
         _p(q), _p(pages), _p(out), _p(decode_seg), c_int(n_decode), _p(part_o), _p(part_ml), c_int(n_spans),
         _p(seg_start), _p(seg_len), _p(seg_pos0), _p(seg_row), _p(block_table), c_int(block_table.shape[1]),
         c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window),
-        c_float(scale), _stream()), "attention (single tokens)")
+        c_float(scale), _stream()), "attention (single tokens)", kernels=2)
 
 
 def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):

@@ -39,9 +39,19 @@ def dtype_code(dtype) -> int:
         raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
 
 
-def _check(lib, code, what):
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module since import (graph replays are counted by their owner)."""
+    return _launches
+
+
+def _check(lib, code, what, kernels=1):
+    global _launches
     if code != 0:
         raise KernelError(f"{what}: {lib.qil_last_error().decode()} (code {code})")
+    _launches += kernels
 
 
 def _p(tensor):
