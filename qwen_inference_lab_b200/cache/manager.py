@@ -75,7 +75,10 @@ class _KVGroup:
 
     @property
     def unreserved(self):
-        return self.capacity - sum(self.reserved.values())
+        """Pages neither promised to a reserved request nor held by an unreserved one."""
+        held_without_credit = sum(sum(1 for p in table if p >= 0)
+                                  for rid, table in self.tables.items() if rid not in self.reserved)
+        return self.capacity - sum(self.reserved.values()) - held_without_credit
 
 
 class CacheManager:
@@ -185,10 +188,14 @@ class CacheManager:
             needed = g.pages_for(end) - len(table)
             if needed <= 0:
                 continue
-            if needed > len(g.free):
-                if limit is not None:
-                    raise RuntimeError("cache reservation invariant violated")
-                raise OutOfPages(f"request {request_id!r} needs {needed} more pages, {len(g.free)} are free")
+            if limit is None:
+                # pages promised to reserved requests but not taken yet are not for the taking
+                promised = sum(credit - sum(1 for p in g.tables[rid] if p >= 0) for rid, credit in g.reserved.items())
+                if needed > len(g.free) - promised:
+                    raise OutOfPages(f"request {request_id!r} needs {needed} more pages, "
+                                     f"{len(g.free) - promised} are free and unpromised")
+            elif needed > len(g.free):
+                raise RuntimeError("cache reservation invariant violated")
             for _ in range(needed):
                 page = g.free.popleft()
                 g.host_table[row, len(table)] = page

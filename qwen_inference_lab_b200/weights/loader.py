@@ -42,7 +42,7 @@ def load_weights(model, directory, *, device, dtype) -> None:
     if not files:
         raise WeightError(f"no safetensors weights found in {directory}")
     unexpected, duplicate, wrong_shape, inconsistent, unreadable = [], [], [], [], []
-    seen_names = set()
+    seen_names, mis_shaped = set(), set()
     for param in set(expected.values()):
         param.data = None
     for path in files:
@@ -63,6 +63,7 @@ def load_weights(model, directory, *, device, dtype) -> None:
                 seen_names.add(name)
                 if tuple(shard.shape(name)) != param.shape:
                     wrong_shape.append(f"{name}: file has {list(shard.shape(name))}, model needs {list(param.shape)}")
+                    mis_shaped.add(id(param))
                     continue
                 source = shard.tensor(name)
                 target = storage_dtype(source.dtype, dtype, param.integer)
@@ -73,8 +74,8 @@ def load_weights(model, directory, *, device, dtype) -> None:
                         inconsistent.append(name)
                     continue
                 param.data = value
-    missing = sorted(name for name, param in expected.items() if param.data is None)
-    # a tied parameter is satisfied by either of its names
+    # a tied parameter is satisfied by either of its names; a mis-shaped tensor is reported as such, not as missing
+    missing = sorted(name for name, param in expected.items() if param.data is None and id(param) not in mis_shaped)
     problems = []
     if missing:
         problems.append(f"missing tensors ({len(missing)}): {missing}")
