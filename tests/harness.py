@@ -192,3 +192,73 @@ def assert_rows_close(actual, expected, dtype, what="", yardstick=None):
             f"{what}: bfloat16 logits are further from the float32 rows than 1.5x the plain bfloat16 "
             f"arithmetic: first wrong (request, position) = {bad[0] if bad else None}, worst = {worst}, "
             f"mean rms {mean_rms:.3e} (bar {bar_rms:.3e}), peak {peak(actual, worst):.3e} (bar {bar_peak:.3e})")
+
+
+# ----------------------------------------------------------------------------- parts alone
+class OnePartModel:
+    """Just enough of a model for the step function to run a single part over a batch.
+
+    ``body(ctx, x, view)`` is called with the rows of ``inputs`` that belong to the step's
+    tokens (request order, then position) and must return a tensor; outputs are collected.
+    """
+
+    def __init__(self, part, hidden, dtype, body, vocab_size=1 << 20, max_positions=4096):
+        from qwen_inference_lab_b200.parts import LayerCall
+        self.part, self.body, self.hidden = part, body, hidden
+        self.device, self.dtype = torch.device("cuda"), dtype
+        self.vocab_size, self.max_positions = vocab_size, max_positions
+        self.order = [LayerCall(0)]
+        self.inputs = None           # [n_inputs, hidden]: token id t of a step selects row t
+        self.outputs = []
+
+    def cache_specs(self):
+        spec = getattr(self.part, "cache_spec", lambda: None)()
+        return [spec]
+
+    def is_graph_safe(self):
+        return False
+
+    def forward(self, ctx, views, logit_rows):
+        x = self.inputs[ctx.token_ids.long()].contiguous()
+        self.outputs.append(self.body(ctx, x, views[0]).float().cpu())
+        return None
+
+
+def run_part(part, hidden, dtype, body, inputs_by_request, cuts, page_size=4, num_pages=64):
+    """Run ``part`` over whole sequences of input rows cut into portions; returns {request: [T, out]}.
+
+    ``inputs_by_request``: {id: tensor [T, hidden]}; ``cuts``: {id: list of portion sizes}.
+    All requests advance together, one portion each per step (a mixed batch).
+    """
+    from qwen_inference_lab_b200.cache import CacheManager
+    from qwen_inference_lab_b200.engine import StepEntry, StepRunner
+    model = OnePartModel(part, hidden, dtype, body)
+    cache = CacheManager(model.cache_specs(), num_pages=num_pages, page_size=page_size, max_requests=4,
+                         max_context=4096, dtype=dtype, device="cuda")
+    cache.poison()
+    runner = StepRunner(model, cache, use_graphs=False)
+    offsets, rows = {}, []
+    for rid, x in inputs_by_request.items():
+        offsets[rid] = sum(r.shape[0] for r in rows)
+        rows.append(x)
+        cache.admit(rid)
+    model.inputs = torch.cat(rows).to(dtype).cuda()
+    done = {rid: 0 for rid in inputs_by_request}
+    portions = {rid: list(sizes) for rid, sizes in cuts.items()}
+    collected = {rid: [] for rid in inputs_by_request}
+    while any(portions.values()):
+        entries, owners = [], []
+        for rid in inputs_by_request:
+            if portions[rid]:
+                size = portions[rid].pop(0)
+                ids = list(range(offsets[rid] + done[rid], offsets[rid] + done[rid] + size))
+                entries.append(StepEntry(rid, ids, []))
+                owners.append((rid, size))
+                done[rid] += size
+        runner.run(entries)
+        out = model.outputs.pop()
+        start = 0
+        for rid, size in owners:
+            collected[rid].append(out[start:start + size])
+            start += size
+    return {rid: torch.cat(parts) for rid, parts in collected.items()}

@@ -1,0 +1,241 @@
+"""An architecture defined here, in the test: registered, built, loaded and stepped with no change
+to the framework's files.  It is a toy, not anyone's model.  Its layers differ in kind:
+
+  0  a mixer with a state of its own (a decaying running sum kept in a per-request slot)
+  1  full attention with q/k norms and full rotation
+  2  attention with a window of 20 positions and rotation of half of each head only
+  3  attention without k/v projections that reads the pages layer 1 wrote
+
+and its order names layer 0 twice: [0, 1, 2, 3, 0].  Each call of layer 0 keeps its own state.
+"""
+import json
+from dataclasses import asdict, dataclass
+
+import pytest
+import torch
+
+from tests import harness
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int = 211
+    width: int = 48
+    state_width: int = 24
+    decay: float = 0.9
+    heads: int = 4
+    kv_heads: int = 2
+    head_dim: int = 16
+    window: int = 20
+    partial_rotary: int = 8
+    theta: float = 10000.0
+    eps: float = 1e-5
+    inner: int = 72
+    max_positions: int = 512
+
+    architecture = "ToyStateLM"
+    model_type = "toy_state"
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(**{k: v for k, v in data.items() if k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return asdict(self) | {"architectures": [self.architecture], "model_type": self.model_type}
+
+
+def make_parts():
+    from qwen_inference_lab_b200.parts import Mixer, Param, StateSpec
+
+    class RunningStateMixer(Mixer):
+        """h_t = decay * h_{t-1} + W_in x_t ;  y_t = W_out h_t.  The state h lives in the request's slot."""
+
+        def __init__(self, width, state_width, decay, *, name):
+            self.decay, self.state_width = decay, state_width
+            self.w_in, self.w_out = Param((state_width, width), std=0.2), Param((width, state_width), std=0.2)
+            self.name = name
+
+        def named_params(self):
+            return {self.name + ".w_in": self.w_in, self.name + ".w_out": self.w_out}
+
+        def cache_spec(self):
+            return StateSpec((self.state_width,), torch.float32)
+
+        def forward(self, ctx, x, cache, residual=None):
+            u = x.float() @ self.w_in.data.float().t()
+            h_all = torch.empty_like(u)
+            for row, start, length in zip(ctx.h_seg_row, ctx.h_seg_start, ctx.h_seg_len):
+                h = cache.slots[row]
+                for t in range(start, start + length):
+                    h = self.decay * h + u[t]
+                    h_all[t] = h
+                cache.slots[row] = h
+            y = (h_all @ self.w_out.data.float().t()).to(x.dtype)
+            return y if residual is None else (residual.float() + y.float()).to(x.dtype)
+
+    return RunningStateMixer
+
+
+def build_toy(config):
+    from qwen_inference_lab_b200.parts import (DecoderModel, GatedMLP, GroupedQueryAttention, LayerCall, Linear,
+                                               PreNormBlock, RMSNorm, RotaryEmbedding, TokenEmbedding)
+    RunningStateMixer = make_parts()
+    w, d = config.width, config.head_dim
+    def block(i, mixer):
+        return PreNormBlock(RMSNorm(w, config.eps, name=f"blocks.{i}.norm_a"), mixer,
+                            RMSNorm(w, config.eps, name=f"blocks.{i}.norm_b"),
+                            GatedMLP(w, config.inner, names={k: f"blocks.{i}.ff.{k}" for k in ("gate", "up", "down")}))
+    def attention(i, **kw):
+        names = {k: f"blocks.{i}.attn.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+        return GroupedQueryAttention(w, config.heads, config.kv_heads, d, names=names, **kw)
+    layers = [
+        block(0, RunningStateMixer(w, config.state_width, config.decay, name="blocks.0.state")),
+        block(1, attention(1, qk_norm_eps=config.eps, position=RotaryEmbedding(d, config.theta, config.max_positions))),
+        block(2, attention(2, qk_norm_eps=config.eps, window=config.window, bias=True,
+                           position=RotaryEmbedding(config.partial_rotary, config.theta, config.max_positions))),
+        block(3, attention(3, reads_shared_cache=True, position=RotaryEmbedding(d, config.theta, config.max_positions))),
+    ]
+    embedding = TokenEmbedding(config.vocab_size, w, name="embed")
+    return DecoderModel(config=config, embedding=embedding, layers=layers,
+                        order=[LayerCall(0), LayerCall(1), LayerCall(2), LayerCall(3, reads_cache_of=1), LayerCall(0)],
+                        final_norm=RMSNorm(w, config.eps, name="final_norm"),
+                        head=Linear(w, config.vocab_size, name="head", weight=embedding.weight),
+                        max_positions=config.max_positions)
+
+
+# ------------------------------------------------------------------ the toy, written plainly for whole sequences
+def toy_plain_logits(tokens, w, c: ToyConfig):
+    T = len(tokens)
+    x = w["embed.weight"][torch.as_tensor(tokens)]
+    positions = torch.arange(T)
+    kv_of_layer1 = {}
+
+    def ff(i, x):
+        n = plain.rms_norm(x, w[f"blocks.{i}.norm_b.weight"], c.eps)
+        gate = torch.nn.functional.silu(plain.linear(n, w[f"blocks.{i}.ff.gate.weight"]))
+        return x + plain.linear(gate * plain.linear(n, w[f"blocks.{i}.ff.up.weight"]), w[f"blocks.{i}.ff.down.weight"])
+
+    def state_layer(x):
+        n = plain.rms_norm(x, w["blocks.0.norm_a.weight"], c.eps)
+        u = n @ w["blocks.0.state.w_in"].t()
+        h, rows = torch.zeros(c.state_width), []
+        for t in range(T):
+            h = c.decay * h + u[t]
+            rows.append(h)
+        return ff(0, x + torch.stack(rows) @ w["blocks.0.state.w_out"].t())
+
+    def rotate_part(v, rotary_dim):
+        angles = plain.rotary_angles(positions, rotary_dim, c.theta)
+        return torch.cat((plain.rotate(v[..., :rotary_dim], angles), v[..., rotary_dim:]), dim=-1)
+
+    def attention_layer(i, x, norms, rotary_dim, window=0, shared=False, bias=False):
+        n = plain.rms_norm(x, w[f"blocks.{i}.norm_a.weight"], c.eps)
+        b = lambda k: w.get(f"blocks.{i}.attn.{k}.bias") if bias else None
+        q = plain.linear(n, w[f"blocks.{i}.attn.q.weight"], b("q")).reshape(T, c.heads, c.head_dim)
+        if norms:
+            q = plain.rms_norm(q, w[f"blocks.{i}.attn.q_norm.weight"], c.eps)
+        q = rotate_part(q, rotary_dim)
+        if shared:
+            k, v = kv_of_layer1["k"], kv_of_layer1["v"]
+        else:
+            k = plain.linear(n, w[f"blocks.{i}.attn.k.weight"], b("k")).reshape(T, c.kv_heads, c.head_dim)
+            v = plain.linear(n, w[f"blocks.{i}.attn.v.weight"], b("v")).reshape(T, c.kv_heads, c.head_dim)
+            if norms:
+                k = plain.rms_norm(k, w[f"blocks.{i}.attn.k_norm.weight"], c.eps)
+            k = rotate_part(k, rotary_dim)
+            if i == 1:
+                kv_of_layer1.update(k=k, v=v)
+        out = plain.causal_attention(q, k, v, c.head_dim ** -0.5, window=window).reshape(T, -1)
+        return ff(i, x + plain.linear(out, w[f"blocks.{i}.attn.o.weight"], b("o")))
+
+    x = state_layer(x)
+    x = attention_layer(1, x, norms=True, rotary_dim=c.head_dim)
+    x = attention_layer(2, x, norms=True, rotary_dim=c.partial_rotary, window=c.window, bias=True)
+    x = attention_layer(3, x, norms=False, rotary_dim=c.head_dim, shared=True)
+    x = state_layer(x)
+    return plain.linear(plain.rms_norm(x, w["final_norm.weight"], c.eps), w["embed.weight"]).float()
+
+
+@pytest.fixture(scope="module")
+def toy(tmp_path_factory):
+    from qwen_inference_lab_b200.config import registry
+    from qwen_inference_lab_b200.weights import SafetensorsFile, write_model_folder
+    registry.register(ToyConfig.architecture, ToyConfig.model_type, ToyConfig, build_toy)
+    try:
+        config = ToyConfig()
+        folder = write_model_folder(config, 11, tmp_path_factory.mktemp("toy"))
+        with SafetensorsFile(folder / "model.safetensors") as f:
+            weights = {name: f.tensor(name).float() for name in f.keys()}
+        yield config, folder, weights
+    finally:
+        registry.unregister(ToyConfig.architecture)
+
+
+def engine_parts(folder, dtype, num_pages=40, page_size=4):
+    from qwen_inference_lab_b200.cache import CacheManager
+    from qwen_inference_lab_b200.engine import StepRunner
+    from qwen_inference_lab_b200.loading import load_model
+    model = load_model(folder, device="cuda", dtype=dtype)
+    cache = CacheManager(model.cache_specs(), num_pages=num_pages, page_size=page_size, max_requests=4,
+                         max_context=model.max_positions, dtype=dtype, device=model.device, max_step_tokens=64)
+    cache.poison()
+    return model, cache, StepRunner(model, cache)
+
+
+def test_toy_is_registered_built_and_loaded(toy):
+    config, folder, weights = toy
+    from qwen_inference_lab_b200.config import registry
+    entry, read_back = registry.read_model_config(folder)
+    assert entry.name == "ToyStateLM" and read_back == config
+    model, cache, runner = engine_parts(folder, torch.float32)
+    assert not model.is_graph_safe() and not runner.use_graphs          # the toy mixer works on the host
+    assert len(cache.state_groups) == 1 and cache.state_groups[0][1] == [0, 4]      # layer 0 twice: two states
+    assert [g.spec.window for g in cache.kv_groups] == [0, 20] and cache.specs[3] is None
+    assert "blocks.3.attn.k.weight" not in weights and "blocks.0.state.w_in" in weights
+
+
+@pytest.mark.parametrize("schedule", ["whole", "tail_decode", "chunks", "mixed"])
+def test_toy_steps_like_its_plain_form_under_every_cut(toy, schedule):
+    config, folder, weights = toy
+    requests = {f"r{i}": torch.randint(0, config.vocab_size, (n,), generator=torch.Generator().manual_seed(i)).tolist()
+                for i, n in enumerate((150, 9, 64, 33, 90))}
+    makers = dict(whole=harness.whole_schedule, tail_decode=harness.tail_decode_schedule,
+                  chunks=harness.chunk_schedule, mixed=harness.mixed_schedule)
+    # pages: the full-attention group must hold whole requests, up to four at a time in the mixed run
+    model, cache, runner = engine_parts(folder, torch.float32, num_pages=4 * 38 if schedule == "mixed" else 38)
+    actual = harness.run_schedule(runner, cache, makers[schedule](requests))
+    assert all(len(g.free) == g.capacity for g in cache.kv_groups)
+    expected = {(rid, p): row for rid, tokens in requests.items()
+                for p, row in enumerate(toy_plain_logits(tokens, weights, config))}
+    harness.assert_rows_close(actual, expected, torch.float32, f"toy {schedule}")
+
+
+def test_window_group_holds_few_pages_while_a_long_request_runs(toy):
+    config, folder, _ = toy
+    model, cache, runner = engine_parts(folder, torch.float32, num_pages=60)
+    tokens = torch.randint(0, config.vocab_size, (200,), generator=torch.Generator().manual_seed(9)).tolist()
+    schedule = harness.chunk_schedule({"r": tokens}, sizes=(16, 7, 2, 5))
+    from qwen_inference_lab_b200.engine import StepEntry
+    cache.admit("r")
+    for entries, _ in schedule:
+        runner.run([StepEntry(rid, t, []) for rid, t, _ in entries])
+        windowed = cache.kv_groups[1]
+        assert sum(1 for p in windowed.tables["r"] if p >= 0) <= (config.window + 16) // 4 + 2
+    assert sum(1 for p in cache.kv_groups[0].tables["r"] if p >= 0) == 50
+    cache.release("r")
+    cache.check_invariants()
+
+
+def test_toy_in_bfloat16_agrees_with_itself_across_cuts(toy):
+    config, folder, weights = toy
+    requests = {"a": torch.randint(0, config.vocab_size, (70,), generator=torch.Generator().manual_seed(3)).tolist()}
+    model, cache, runner = engine_parts(folder, torch.bfloat16)
+    whole = harness.run_schedule(runner, cache, harness.whole_schedule(requests))
+    cut = harness.run_schedule(runner, cache, harness.chunk_schedule(requests))
+    truth = toy_plain_logits(requests["a"], weights, config)
+    for p in range(70):
+        assert (whole[("a", p)] - cut[("a", p)]).abs().max() < 0.05
+        assert (whole[("a", p)] - truth[p]).abs().max() < 0.1
