@@ -1,0 +1,80 @@
+// qil_attn_decode_noalloc: the single-token attention of attention_mma.cu with its
+// scratch in a file-scope device array instead of caller-allocated buffers.
+// See attention_decode_noalloc.h for who needs this and for the rules of use.
+//
+// The kernels are the ones of attention_mma.cu, compiled into this library too.
+#include "attention_mma.cu"
+#include "attention_decode_noalloc.h"
+
+#define QIL_NOALLOC_MAX_FLOATS (4ll * 1024 * 1024)     // 16 MiB
+#define QIL_NOALLOC_MAX_DEVICES 64
+
+// Partial sums of the span kernel, then their (max, sum) pairs.  In host code this name is
+// only a handle for cudaGetSymbolAddress; kernels get the address that call returns.
+static __device__ __align__(256) float qil_noalloc_scratch[QIL_NOALLOC_MAX_FLOATS];
+
+static float* noalloc_scratch_address[QIL_NOALLOC_MAX_DEVICES];   // per device, filled by the first call
+
+extern "C" long long qil_attn_decode_noalloc_max_floats(void) { return QIL_NOALLOC_MAX_FLOATS; }
+
+// Once per device, with that device current: the array's address and the span kernel's
+// shared-memory limit.  Neither allocates.
+static int noalloc_setup(int smem, float** scratch) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "cudaGetDevice: %s", cudaGetErrorString(e)); return (int)e; }
+    if (device < 0 || device >= QIL_NOALLOC_MAX_DEVICES) QIL_REFUSE("attention (no allocation): device %d is out of range", device);
+    if (noalloc_scratch_address[device] == nullptr) {
+        float* address = nullptr;
+        e = cudaGetSymbolAddress((void**)&address, qil_noalloc_scratch);
+        if (e != cudaSuccess || address == nullptr) {
+            snprintf(qil_error_text, sizeof(qil_error_text), "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : -1;
+        }
+        e = cudaFuncSetAttribute(attn_decode_span_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) {
+            snprintf(qil_error_text, sizeof(qil_error_text), "cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+            return (int)e;
+        }
+        noalloc_scratch_address[device] = address;
+    }
+    *scratch = noalloc_scratch_address[device];
+    return 0;
+}
+
+extern "C" int qil_attn_decode_noalloc(const void* q, const void* kv, void* out, const int* decode_seg, int n_decode,
+                                       int n_spans, const int* seg_start, const int* seg_len, const int* seg_pos0,
+                                       const int* seg_row, const int* block_table, int table_stride, int n_q_heads,
+                                       int n_kv_heads, int page_size, int num_pages, int window, float scale,
+                                       cudaStream_t stream) {
+    if (n_decode <= 0) return 0;
+    AttnParams p;
+    if (fill_params(p, q, kv, out, seg_start, seg_len, seg_pos0, seg_row, block_table, table_stride, n_q_heads,
+                    n_kv_heads, page_size, num_pages, window, scale)) return -1;
+    if (n_spans <= 0) QIL_REFUSE("attention (no allocation): n_spans %d", n_spans);
+    const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
+    if (n_kv_heads * chunks > 65535 || n_decode > 65535) QIL_REFUSE("attention (no allocation): grid too large");
+    const long long slots = (long long)n_decode * n_q_heads * n_spans;
+    const long long o_floats = (slots * D + 63) / 64 * 64;          // part_ml starts on a 256-byte boundary
+    const long long needed = o_floats + (slots * 2 + 63) / 64 * 64;
+    if (needed > QIL_NOALLOC_MAX_FLOATS)
+        QIL_REFUSE("attention (no allocation): %d tokens x %d heads x %d spans need %lld floats of scratch, "
+                   "the built-in array holds %lld; use qil_attn_decode with your own buffers",
+                   n_decode, n_q_heads, n_spans, needed, (long long)QIL_NOALLOC_MAX_FLOATS);
+    const int tile_bytes = (16 + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
+    const int merge_bytes = 16 * LDS * (int)sizeof(bf16) + (2 * 4 * 16 + 4 * 16 * D) * (int)sizeof(float);
+    const int smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
+    float* scratch = nullptr;
+    const int status = noalloc_setup(smem, &scratch);
+    if (status != 0) return status;
+    float* part_o = scratch;
+    float* part_ml = scratch + o_floats;
+    attn_decode_span_kernel<<<dim3(n_spans, n_kv_heads * chunks, n_decode), 128, smem, stream>>>(
+        p, decode_seg, part_o, part_ml, n_spans);
+    {
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }
+    }
+    attn_decode_merge_kernel<<<dim3(n_q_heads, n_decode), 128, 0, stream>>>(p, decode_seg, part_o, part_ml, n_spans);
+    QIL_CHECK_LAUNCH();
+}

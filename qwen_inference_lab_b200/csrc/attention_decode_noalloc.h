@@ -1,0 +1,56 @@
+/* Single-token paged attention for callers that cannot allocate device memory.
+ *
+ * This entry point has no counterpart in the reference (provoke210/qwen-inference-lab):
+ * it exists for users of this library, not for parity.
+ *
+ * Who it is for.  The regular entry point, qil_attn_decode, takes two scratch
+ * buffers that its caller allocates.  Some callers have nowhere to get them:
+ * a host program that gave all device memory to its own pool at start-up and
+ * forbids cudaMalloc afterwards, or a loop that may not stall (cudaMalloc and
+ * cudaFree can synchronise the whole device).  Those callers use this function:
+ * it keeps its scratch in a fixed array inside the library.
+ *
+ * What it does.  The same computation as qil_attn_decode, with the same kernels
+ * and the same arguments minus the two scratch pointers: attention of n_decode
+ * single tokens over their requests' paged keys and values (bfloat16, head size
+ * fixed when the library was compiled).  q, kv, out and the int arrays are the
+ * caller's; out receives [token, head, head_dim] rows of the tokens listed in
+ * decode_seg.
+ *
+ * Limits and rules.
+ *  - The scratch array holds qil_attn_decode_noalloc_max_floats() floats (16 MiB;
+ *    every GPU that loads the library holds that much until the process exits).
+ *    A call needs  n_decode * n_q_heads * n_spans * (head_dim + 2)  floats, rounded up
+ *    to a multiple of 64; a call that needs more returns -1 and qil_last_error()
+ *    says by how much.  Nothing is launched in that case.
+ *  - It calls no cudaMalloc, cudaFree or any routine that allocates.
+ *  - The first call on each device looks up the array's device address and sets
+ *    a kernel attribute; make that first call outside any stream capture, with
+ *    the device it is meant for current.
+ *  - All calls share the one array, and it keeps what the last call left in it.
+ *    Nothing in it has to start at zero: every slot a call reads, that call wrote
+ *    first.  Two calls whose kernels overlap on the GPU (different streams, no
+ *    ordering between them) race on the array; order them.
+ *
+ * Returns 0 when the kernels were queued on `stream`, a positive cudaError_t if a
+ * CUDA call failed, -1 if the arguments were refused.
+ */
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int qil_attn_decode_noalloc(const void* q, const void* kv, void* out, const int* decode_seg, int n_decode,
+                            int n_spans, const int* seg_start, const int* seg_len, const int* seg_pos0,
+                            const int* seg_row, const int* block_table, int table_stride, int n_q_heads,
+                            int n_kv_heads, int page_size, int num_pages, int window, float scale,
+                            cudaStream_t stream);
+
+/* Capacity of the built-in scratch array, in floats. */
+long long qil_attn_decode_noalloc_max_floats(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -58,9 +58,9 @@ def build_dir() -> Path:
     raise KernelBuildError("no writable folder for compiled kernels")
 
 
-def _digest(sources, defines, flags) -> str:
+def _digest(sources, defines, flags, depends=()) -> str:
     h = hashlib.sha256()
-    for path in sorted(CSRC.glob("*.cuh")) + [CSRC / s for s in sources]:
+    for path in sorted(CSRC.glob("*.cuh")) + [CSRC / s for s in list(sources) + list(depends)]:
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(repr(sorted(defines.items())).encode())
@@ -68,11 +68,12 @@ def _digest(sources, defines, flags) -> str:
     return h.hexdigest()[:16]
 
 
-def library_path(name: str, sources, defines=None) -> tuple:
+def library_path(name: str, sources, defines=None, depends=()) -> tuple:
+    """``depends``: files under csrc/ that the sources include beside the ``.cuh`` headers."""
     defines = dict(defines or {})
     extra = os.environ.get("QIL_NVCC_FLAGS", "").split()
     flags = ARCH_FLAGS + BASE_FLAGS + extra
-    tag = _digest(sources, defines, flags)
+    tag = _digest(sources, defines, flags, depends)
     return f"{name}-{tag}.so", flags, defines
 
 
@@ -106,9 +107,9 @@ def _run_with_progress(commands, label):
             print(out, file=sys.stderr)
 
 
-def build(name: str, sources, defines=None) -> Path:
+def build(name: str, sources, defines=None, depends=()) -> Path:
     """Return the path of the compiled library, compiling it first if need be."""
-    filename, flags, defines = library_path(name, sources, defines)
+    filename, flags, defines = library_path(name, sources, defines, depends)
     found = _find_built(filename)
     if found is not None:
         return found
@@ -139,12 +140,12 @@ def build(name: str, sources, defines=None) -> Path:
     return target
 
 
-def load(name: str, sources, defines=None) -> ctypes.CDLL:
+def load(name: str, sources, defines=None, depends=()) -> ctypes.CDLL:
     key = (name, tuple(sources), tuple(sorted((defines or {}).items())))
     with _lock:
         lib = _loaded.get(key)
         if lib is None:
-            path = build(name, sources, defines)
+            path = build(name, sources, defines, depends)
             lib = ctypes.CDLL(str(path))
             lib.qil_last_error.restype = ctypes.c_char_p
             lib._qil_path = str(path)
