@@ -42,16 +42,16 @@ static int noalloc_setup(int smem, float** scratch) {
     return 0;
 }
 
-extern "C" int qil_attn_decode_noalloc(const void* q, const void* kv, void* out, const int* decode_seg, int n_decode,
-                                       int n_spans, const int* seg_start, const int* seg_len, const int* seg_pos0,
-                                       const int* seg_row, const int* block_table, int table_stride, int n_q_heads,
-                                       int n_kv_heads, int page_size, int num_pages, int window, float scale,
-                                       cudaStream_t stream) {
+extern "C" int qil_attn_decode_noalloc(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
+                                       int n_spans, int span_len, const int* block_table, int table_stride,
+                                       int n_q_heads, int n_kv_heads, int page_size, int num_pages, int window,
+                                       float scale, cudaStream_t stream) {
     if (n_decode <= 0) return 0;
     AttnParams p;
-    if (fill_params(p, q, kv, out, seg_start, seg_len, seg_pos0, seg_row, block_table, table_stride, n_q_heads,
-                    n_kv_heads, page_size, num_pages, window, scale)) return -1;
-    if (n_spans <= 0) QIL_REFUSE("attention (no allocation): n_spans %d", n_spans);
+    if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
+                    window, scale)) return -1;
+    if (check_decode_span(span_len, n_spans)) return -1;
+    if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention (no allocation): decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
     if (n_kv_heads * chunks > 65535 || n_decode > 65535) QIL_REFUSE("attention (no allocation): grid too large");
     const long long slots = (long long)n_decode * n_q_heads * n_spans;
@@ -61,20 +61,21 @@ extern "C" int qil_attn_decode_noalloc(const void* q, const void* kv, void* out,
         QIL_REFUSE("attention (no allocation): %d tokens x %d heads x %d spans need %lld floats of scratch, "
                    "the built-in array holds %lld; use qil_attn_decode with your own buffers",
                    n_decode, n_q_heads, n_spans, needed, (long long)QIL_NOALLOC_MAX_FLOATS);
-    const int tile_bytes = (16 + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
-    const int merge_bytes = 16 * LDS * (int)sizeof(bf16) + (2 * 4 * 16 + 4 * 16 * D) * (int)sizeof(float);
-    const int smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
+    // the largest shared memory any legal span can ask for, so that one set-up serves every later call
+    const int smem_limit = decode_smem_bytes(MAX_DECODE_SPAN, 1);
+    const int smem = decode_smem_bytes(span_len, page_size);
     float* scratch = nullptr;
-    const int status = noalloc_setup(smem, &scratch);
+    const int status = noalloc_setup(smem_limit, &scratch);
     if (status != 0) return status;
     float* part_o = scratch;
     float* part_ml = scratch + o_floats;
     attn_decode_span_kernel<<<dim3(n_spans, n_kv_heads * chunks, n_decode), 128, smem, stream>>>(
-        p, decode_seg, part_o, part_ml, n_spans);
+        p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len);
     {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }
     }
-    attn_decode_merge_kernel<<<dim3(n_q_heads, n_decode), 128, 0, stream>>>(p, decode_seg, part_o, part_ml, n_spans);
+    attn_decode_merge_kernel<<<dim3(n_q_heads, n_decode), 128, 0, stream>>>(p, (const int4*)decode_info, part_o,
+                                                                           part_ml, n_spans, span_len);
     QIL_CHECK_LAUNCH();
 }

@@ -14,8 +14,10 @@
  * and the same arguments minus the two scratch pointers: attention of n_decode
  * single tokens over their requests' paged keys and values (bfloat16, head size
  * fixed when the library was compiled).  q, kv, out and the int arrays are the
- * caller's; out receives [token, head, head_dim] rows of the tokens listed in
- * decode_seg.
+ * caller's; decode_info holds four ints per token (its row in q and out, its
+ * absolute position, its row of the block table, 0); span_len is the number of
+ * key positions one block covers (a multiple of 64) and n_spans * span_len must
+ * reach the longest context.
  *
  * Limits and rules.
  *  - The scratch array holds qil_attn_decode_noalloc_max_floats() floats (16 MiB;
@@ -42,11 +44,10 @@
 extern "C" {
 #endif
 
-int qil_attn_decode_noalloc(const void* q, const void* kv, void* out, const int* decode_seg, int n_decode,
-                            int n_spans, const int* seg_start, const int* seg_len, const int* seg_pos0,
-                            const int* seg_row, const int* block_table, int table_stride, int n_q_heads,
-                            int n_kv_heads, int page_size, int num_pages, int window, float scale,
-                            cudaStream_t stream);
+int qil_attn_decode_noalloc(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
+                            int n_spans, int span_len, const int* block_table, int table_stride,
+                            int n_q_heads, int n_kv_heads, int page_size, int num_pages, int window,
+                            float scale, cudaStream_t stream);
 
 /* Capacity of the built-in scratch array, in floats. */
 long long qil_attn_decode_noalloc_max_floats(void);

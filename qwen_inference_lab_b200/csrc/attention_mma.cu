@@ -11,14 +11,16 @@
 //    shared memory in tiles of 64 positions, found through the block table, with
 //    an online softmax; history written by earlier steps and the portion's own
 //    keys are treated alike.
-//  * single tokens: one block per (span of 256 positions, kv head, token) serves
+//  * single tokens: one block per (span of positions, kv head, token) serves
 //    all query heads of that kv head at once, so every key byte is read once;
 //    blocks write unnormalised partial sums and (max, sum) to scratch memory and
 //    a second kernel merges the spans in ascending order
 //    (the reference's partition + merge kernels, qil/paged_attention.py:13-58).
+//    The span length is the caller's choice (a multiple of 64): short spans fill
+//    the GPU when few tokens decode, long spans amortise a block's start-up when
+//    many do.
 //
-// Key tiles and spans are aligned to absolute positions, so a token's result
-// does not depend on the batch it is in.
+// Key tiles and spans are aligned to absolute positions.
 // Cache layout of one layer: [page][2 (K,V)][kv_head][slot in page][head_dim].
 #include "common.cuh"
 
@@ -32,7 +34,7 @@ QIL_ERROR_STORAGE
 
 #define KV_TILE 64          // key positions per shared-memory tile
 #define Q_TILE 64           // query tokens per block (prompt portions)
-#define DECODE_SPAN 256     // key positions per block (single tokens)
+#define MAX_DECODE_SPAN 2048 // most key positions per block (single tokens)
 
 constexpr int D = QIL_HEAD_DIM;
 constexpr int LDS = D + 8;           // shared-memory row stride in elements: rows start 16 bytes apart mod 128
@@ -72,44 +74,45 @@ struct AttnParams {
     const bf16* q;            // [N, Hq, D]
     const bf16* kv;           // one layer's pages
     bf16* out;                // [N, Hq, D]
-    const int* seg_start;
-    const int* seg_len;
-    const int* seg_pos0;
-    const int* seg_row;
     const int* block_table;
     int table_stride;
     int n_q_heads, n_kv_heads, page_size, num_pages, window;
     float scale_log2;         // head_dim^-1/2 * log2(e)
 };
 
-// Load 64 key rows and 64 value rows (positions tile*64 ...) of one kv head into shared memory.
-// Two threads per row; rows outside [lo, hi] or without a page are zero-filled.
-__device__ __forceinline__ void load_kv_tile(const AttnParams& p, const int* table, int kv_head, int tile,
-                                             int lo, int hi, bf16* sK, bf16* sV, int tid) {
-    const int row = tid >> 1, half = tid & 1;
-    const int pos = tile * KV_TILE + row;
-    bool valid = pos >= lo && pos <= hi;
-    size_t offset = 0;
-    if (valid) {
-        const int page = table[pos / p.page_size];
-        valid = page >= 0 && page < p.num_pages;
-        if (valid)
-            offset = ((((size_t)page * 2) * p.n_kv_heads + kv_head) * p.page_size + (pos % p.page_size)) * D;
-    }
-    const bf16* k_src = p.kv + offset;
-    const bf16* v_src = k_src + (size_t)p.n_kv_heads * p.page_size * D;
-    constexpr int CHUNKS = D / 16;   // 16-byte chunks per thread per row
+// Where the key row of position ``pos`` of one kv head starts, in units of 16 bytes from the layer's
+// base (the value row lies one (kv_heads * page_size * D) plane further); -1 when the position is outside
+// [lo, hi] or holds no page.  ``pages`` holds the request's page ids from logical page ``first_page`` on.
+__device__ __forceinline__ int kv_row_offset(const AttnParams& p, const int* pages, int first_page, int kv_head,
+                                             int pos, int lo, int hi) {
+    if (pos < lo || pos > hi) return -1;
+    const int page = pages[pos / p.page_size - first_page];
+    if (page < 0 || page >= p.num_pages) return -1;
+    return (int)((((size_t)page * 2 * p.n_kv_heads + kv_head) * p.page_size + (pos % p.page_size)) * (D / 8));
+}
+
+// Queue the copies of 64 key rows and 64 value rows into shared memory; rows without an offset are
+// zero-filled.  Consecutive threads take consecutive 16-byte pieces of a row, so one warp request
+// covers whole 128-byte lines (a request that touches 32 different lines costs 32 tag look-ups).
+__device__ __forceinline__ void issue_kv_tile(const AttnParams& p, const int* row_off, bf16* sK, bf16* sV, int tid) {
+    constexpr int CPR = D / 8;                  // 16-byte pieces per row
+    constexpr int PASSES = KV_TILE * CPR / 128; // D is a multiple of 16, so this is exact
+    const size_t v_plane = (size_t)p.n_kv_heads * p.page_size * D;
 #pragma unroll
-    for (int c = 0; c < CHUNKS; ++c) {
-        const int col = (half * CHUNKS + c) * 8;
-        cp_async16(sK + row * LDS + col, k_src + col, valid);
-        cp_async16(sV + row * LDS + col, v_src + col, valid);
+    for (int i = 0; i < PASSES; ++i) {
+        const int idx = i * 128 + tid;
+        const int row = idx / CPR, piece = idx % CPR;
+        const int off = row_off[row];
+        const bool valid = off >= 0;
+        const bf16* src = p.kv + (size_t)(valid ? off : 0) * 8 + piece * 8;
+        cp_async16(sK + row * LDS + piece * 8, src, valid);
+        cp_async16(sV + row * LDS + piece * 8, src + v_plane, valid);
     }
 }
 
 // ------------------------------------------------------------------ prompt portions
 __global__ void __launch_bounds__(128)
-attn_prefill_kernel(AttnParams p, const int* __restrict__ tile_seg, const int* __restrict__ tile_off) {
+attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [64][LDS]
     bf16* sK = sQ + Q_TILE * LDS;                       // [2][64][LDS]
@@ -117,13 +120,12 @@ attn_prefill_kernel(AttnParams p, const int* __restrict__ tile_seg, const int* _
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int head = blockIdx.y;
     const int kv_head = head / (p.n_q_heads / p.n_kv_heads);
-    const int seg = tile_seg[blockIdx.x], off = tile_off[blockIdx.x];
-    const int rows = min(Q_TILE, p.seg_len[seg] - off);
-    const int n0 = p.seg_start[seg] + off;
-    const int pos0 = p.seg_pos0[seg] + off;
+    // tile_info: (first token in the flat batch, its absolute position, rows in the tile, block-table row)
+    const int4 info = tile_info[blockIdx.x];
+    const int n0 = info.x, pos0 = info.y, rows = min(Q_TILE, info.z);
     const int hi = pos0 + rows - 1;
     const int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
-    const int* table = p.block_table + (size_t)p.seg_row[seg] * p.table_stride;
+    const int* table = p.block_table + (size_t)info.w * p.table_stride;
 
     {   // queries of this tile: two threads per row
         const int row = tid >> 1, half = tid & 1;
@@ -136,8 +138,14 @@ attn_prefill_kernel(AttnParams p, const int* __restrict__ tile_seg, const int* _
             cp_async16(sQ + row * LDS + col, src + col, valid);
         }
     }
+    __shared__ int row_off[2][KV_TILE];
     const int first_tile = lo / KV_TILE, last_tile = hi / KV_TILE;
-    load_kv_tile(p, table, kv_head, first_tile, lo, hi, sK, sV, tid);
+    if (tid < KV_TILE) {
+        row_off[0][tid] = kv_row_offset(p, table, 0, kv_head, first_tile * KV_TILE + tid, lo, hi);
+        row_off[1][tid] = kv_row_offset(p, table, 0, kv_head, (first_tile + 1) * KV_TILE + tid, lo, hi);
+    }
+    __syncthreads();
+    issue_kv_tile(p, row_off[0], sK, sV, tid);
     cp_async_commit();
 
     unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];
@@ -151,11 +159,13 @@ attn_prefill_kernel(AttnParams p, const int* __restrict__ tile_seg, const int* _
     for (int tile = first_tile; tile <= last_tile; ++tile) {
         const int buf = (tile - first_tile) & 1;
         if (tile + 1 <= last_tile)
-            load_kv_tile(p, table, kv_head, tile + 1, lo, hi, sK + (buf ^ 1) * KV_TILE * LDS,
-                         sV + (buf ^ 1) * KV_TILE * LDS, tid);
+            issue_kv_tile(p, row_off[buf ^ 1], sK + (buf ^ 1) * KV_TILE * LDS, sV + (buf ^ 1) * KV_TILE * LDS, tid);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
+        // the row offsets of the tile after next go where this tile's were (everyone has used those)
+        if (tile + 2 <= last_tile && tid < KV_TILE)
+            row_off[buf][tid] = kv_row_offset(p, table, 0, kv_head, (tile + 2) * KV_TILE + tid, lo, hi);
         if (Q_IN_REGS && tile == first_tile) {
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks)
@@ -254,29 +264,31 @@ attn_prefill_kernel(AttnParams p, const int* __restrict__ tile_seg, const int* _
 }
 
 // ------------------------------------------------------------------ single tokens: spans
+// decode_info: (token in the flat batch, its absolute position, block-table row, unused) per token.
 // part_o  [n_decode, Hq, n_spans, D] float32, unnormalised; part_ml [n_decode, Hq, n_spans, 2] (max, sum).
 __global__ void __launch_bounds__(128)
-attn_decode_span_kernel(AttnParams p, const int* __restrict__ decode_seg, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int n_spans) {
+attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int n_spans, int span_len) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [16][LDS]
     bf16* sK = sQ + 16 * LDS;                           // [2][64][LDS]
     bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
+    int* s_pages = reinterpret_cast<int*>(sV + 2 * KV_TILE * LDS);   // [span_len / page_size + 2]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = p.n_q_heads / p.n_kv_heads;
     const int chunks = (group + 15) / 16;
     const int kv_head = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * 16;
     const int gcount = min(16, group - g0);
     const int span = blockIdx.x, d_idx = blockIdx.z;
-    const int seg = decode_seg[d_idx];
-    const int n = p.seg_start[seg], pos = p.seg_pos0[seg];
+    const int4 info = decode_info[d_idx];
+    const int n = info.x, pos = info.y;
     const int hi = pos;
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    const int k_begin = span * DECODE_SPAN;
-    if (k_begin > hi || k_begin + DECODE_SPAN <= lo) return;    // the merge skips the same spans
-    const int* table = p.block_table + (size_t)p.seg_row[seg] * p.table_stride;
+    const int k_begin = span * span_len;
+    if (k_begin > hi || k_begin + span_len <= lo) return;    // the merge skips the same spans
+    const int* table = p.block_table + (size_t)info.z * p.table_stride;
     const int first_tile = max(k_begin, lo) / KV_TILE;
-    const int last_tile = min(k_begin + DECODE_SPAN - 1, hi) / KV_TILE;
+    const int last_tile = min(k_begin + span_len - 1, hi) / KV_TILE;
 
     {   // the query heads of this kv head: 8 threads per row
         const int row = tid >> 3;
@@ -284,7 +296,19 @@ attn_decode_span_kernel(AttnParams p, const int* __restrict__ decode_seg, float*
         const bf16* src = p.q + ((size_t)n * p.n_q_heads + kv_head * group + g0 + (valid ? row : 0)) * D;
         for (int c = tid & 7; c < D / 8; c += 8) cp_async16(sQ + row * LDS + c * 8, src + c * 8, valid);
     }
-    load_kv_tile(p, table, kv_head, first_tile, lo, hi, sK, sV, tid);
+    // the page ids of the whole span, once: a tile's loads then wait for no table read
+    const int first_page = (first_tile * KV_TILE) / p.page_size;
+    const int last_page = min((last_tile + 1) * KV_TILE - 1, hi) / p.page_size;
+    for (int i = tid; i <= last_page - first_page; i += 128) s_pages[i] = table[first_page + i];
+    __syncthreads();
+    __shared__ int row_off[2][KV_TILE];
+    if (tid < KV_TILE) {
+        row_off[0][tid] = kv_row_offset(p, s_pages, first_page, kv_head, first_tile * KV_TILE + tid, lo, hi);
+        row_off[1][tid] = kv_row_offset(p, s_pages, first_page, kv_head, (first_tile + 1) * KV_TILE + tid, lo,
+                                        min(hi, (last_tile + 1) * KV_TILE - 1));
+    }
+    __syncthreads();
+    issue_kv_tile(p, row_off[0], sK, sV, tid);
     cp_async_commit();
 
     unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];
@@ -296,11 +320,12 @@ attn_decode_span_kernel(AttnParams p, const int* __restrict__ decode_seg, float*
     for (int tile = first_tile; tile <= last_tile; ++tile) {
         const int buf = (tile - first_tile) & 1;
         if (tile + 1 <= last_tile)
-            load_kv_tile(p, table, kv_head, tile + 1, lo, hi, sK + (buf ^ 1) * KV_TILE * LDS,
-                         sV + (buf ^ 1) * KV_TILE * LDS, tid);
+            issue_kv_tile(p, row_off[buf ^ 1], sK + (buf ^ 1) * KV_TILE * LDS, sV + (buf ^ 1) * KV_TILE * LDS, tid);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
+        if (tile + 2 <= last_tile && tid < KV_TILE)
+            row_off[buf][tid] = kv_row_offset(p, s_pages, first_page, kv_head, (tile + 2) * KV_TILE + tid, lo, hi);
         if (Q_IN_REGS && tile == first_tile) {
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks)
@@ -410,14 +435,14 @@ attn_decode_span_kernel(AttnParams p, const int* __restrict__ decode_seg, float*
 
 // ------------------------------------------------------------------ single tokens: merge of the spans
 __global__ void __launch_bounds__(128)
-attn_decode_merge_kernel(AttnParams p, const int* __restrict__ decode_seg, const float* __restrict__ part_o,
-                         const float* __restrict__ part_ml, int n_spans) {
+attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, const float* __restrict__ part_o,
+                         const float* __restrict__ part_ml, int n_spans, int span_len) {
     const int head = blockIdx.x, d_idx = blockIdx.y;
-    const int seg = decode_seg[d_idx];
-    const int n = p.seg_start[seg], pos = p.seg_pos0[seg];
+    const int4 info = decode_info[d_idx];
+    const int n = info.x, pos = info.y;
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    const int s_lo = lo / DECODE_SPAN;
-    int s_hi = pos / DECODE_SPAN;
+    const int s_lo = lo / span_len;
+    int s_hi = pos / span_len;
     if (s_hi >= n_spans) s_hi = n_spans - 1;   // cannot happen when the host sized n_spans for the batch
     const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
     float mx = -INFINITY;
@@ -435,8 +460,7 @@ attn_decode_merge_kernel(AttnParams p, const int* __restrict__ decode_seg, const
 }
 
 // ------------------------------------------------------------------ entry points
-static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, const int* seg_start,
-                       const int* seg_len, const int* seg_pos0, const int* seg_row, const int* block_table,
+static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, const int* block_table,
                        int table_stride, int n_q_heads, int n_kv_heads, int page_size, int num_pages,
                        int window, float scale) {
     if (n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads)
@@ -446,7 +470,6 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
     if (((uintptr_t)q | (uintptr_t)kv | (uintptr_t)out) & 15)
         QIL_REFUSE("attention: q, cache and out must be 16-byte aligned");
     p.q = (const bf16*)q; p.kv = (const bf16*)kv; p.out = (bf16*)out;
-    p.seg_start = seg_start; p.seg_len = seg_len; p.seg_pos0 = seg_pos0; p.seg_row = seg_row;
     p.block_table = block_table; p.table_stride = table_stride;
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window;
@@ -454,19 +477,33 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
     return 0;
 }
 
-extern "C" int qil_attn_head_dim() { return D; }
-extern "C" int qil_attn_decode_span() { return DECODE_SPAN; }
+// Shared memory of the span kernel: query rows, two stages of key and value tiles (reused for the
+// merge of the four warps), and the span's page ids.
+static int decode_smem_bytes(int span_len, int page_size) {
+    const int tile_bytes = (16 + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
+    return tile_bytes + (span_len / page_size + 3) * (int)sizeof(int);
+}
 
-extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const int* tile_seg, const int* tile_off,
-                                int n_tiles, const int* seg_start, const int* seg_len, const int* seg_pos0,
-                                const int* seg_row, const int* block_table, int table_stride, int n_q_heads,
-                                int n_kv_heads, int page_size, int num_pages, int window, float scale,
-                                cudaStream_t stream) {
+static int check_decode_span(int span_len, int n_spans) {
+    if (span_len < KV_TILE || span_len > MAX_DECODE_SPAN || span_len % KV_TILE)
+        QIL_REFUSE("attention: a span of %d positions; spans are multiples of %d up to %d", span_len, KV_TILE, MAX_DECODE_SPAN);
+    if (n_spans <= 0) QIL_REFUSE("attention: n_spans %d", n_spans);
+    return 0;
+}
+
+extern "C" int qil_attn_head_dim() { return D; }
+extern "C" int qil_attn_max_decode_span() { return MAX_DECODE_SPAN; }
+
+// tile_info: int32 [n_tiles, 4] = (first token, its absolute position, rows <= 64, block-table row).
+extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     AttnParams p;
-    if (fill_params(p, q, kv, out, seg_start, seg_len, seg_pos0, seg_row, block_table, table_stride, n_q_heads,
-                    n_kv_heads, page_size, num_pages, window, scale)) return -1;
+    if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
+                    window, scale)) return -1;
     if (n_q_heads > 65535) QIL_REFUSE("attention: too many heads (%d)", n_q_heads);
+    if ((uintptr_t)tile_info & 15) QIL_REFUSE("attention: tile_info must be 16-byte aligned");
     const int smem = (Q_TILE + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
     static bool configured = false;
     if (!configured) {
@@ -474,39 +511,40 @@ extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const 
         if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    attn_prefill_kernel<<<dim3(n_tiles, n_q_heads), 128, smem, stream>>>(p, tile_seg, tile_off);
+    attn_prefill_kernel<<<dim3(n_tiles, n_q_heads), 128, smem, stream>>>(p, (const int4*)tile_info);
     QIL_CHECK_LAUNCH();
 }
 
+// decode_info: int32 [n_decode, 4] = (token, its absolute position, block-table row, 0).
 // Scratch: part_o needs n_decode * Hq * n_spans * D floats, part_ml n_decode * Hq * n_spans * 2 floats.
-// n_spans must cover the longest context of the batch: ceil(max(position + 1) / DECODE_SPAN).
-extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const int* decode_seg, int n_decode,
-                               float* part_o, float* part_ml, int n_spans, const int* seg_start,
-                               const int* seg_len, const int* seg_pos0, const int* seg_row,
+// n_spans * span_len must cover the longest context of the batch (max position + 1).
+extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
+                               float* part_o, float* part_ml, int n_spans, int span_len,
                                const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                                int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
     if (n_decode <= 0) return 0;
     AttnParams p;
-    if (fill_params(p, q, kv, out, seg_start, seg_len, seg_pos0, seg_row, block_table, table_stride, n_q_heads,
-                    n_kv_heads, page_size, num_pages, window, scale)) return -1;
-    if (n_spans <= 0 || part_o == nullptr || part_ml == nullptr) QIL_REFUSE("attention: decode needs scratch for %d spans", n_spans);
+    if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
+                    window, scale)) return -1;
+    if (check_decode_span(span_len, n_spans)) return -1;
+    if (part_o == nullptr || part_ml == nullptr) QIL_REFUSE("attention: decode needs scratch for %d spans", n_spans);
+    if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention: decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
     if (n_kv_heads * chunks > 65535 || n_decode > 65535) QIL_REFUSE("attention: grid too large");
-    const int tile_bytes = (16 + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
-    const int merge_bytes = 16 * LDS * (int)sizeof(bf16) + (2 * 4 * 16 + 4 * 16 * D) * (int)sizeof(float);
-    const int smem = tile_bytes > merge_bytes ? tile_bytes : merge_bytes;
-    static bool configured = false;
-    if (!configured) {
+    const int smem = decode_smem_bytes(span_len, page_size);
+    static int configured = 0;
+    if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_span_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
+        configured = smem;
     }
     attn_decode_span_kernel<<<dim3(n_spans, n_kv_heads * chunks, n_decode), 128, smem, stream>>>(
-        p, decode_seg, part_o, part_ml, n_spans);
+        p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len);
     {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }
     }
-    attn_decode_merge_kernel<<<dim3(n_q_heads, n_decode), 128, 0, stream>>>(p, decode_seg, part_o, part_ml, n_spans);
+    attn_decode_merge_kernel<<<dim3(n_q_heads, n_decode), 128, 0, stream>>>(p, (const int4*)decode_info, part_o,
+                                                                           part_ml, n_spans, span_len);
     QIL_CHECK_LAUNCH();
 }

@@ -66,17 +66,21 @@ extern "C" int qil_rmsnorm(const void* x, const void* weight, const int* rows, v
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
-// gate_up: [n_rows, 2 * width] (gate columns first, then up); out: [n_rows, width].
+// gate_up: [n_rows, 2 * width]; out: [n_rows, width].  pairs8 == 0: gate columns first, then up
+// columns.  pairs8 == 1: groups of 16 columns, 8 gate columns then the 8 matching up columns
+// (the layout the decode GEMM's fused epilogue wants its weight rows in).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width,
-                                size_t total) {
+                                size_t total, int pairs8) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
         const size_t row = i / width;
         const int col = (int)(i - row * width);
-        const float g = to_f32<T>(gate_up[row * 2 * width + col]);
-        const float u = to_f32<T>(gate_up[row * 2 * width + width + col]);
+        const int gcol = pairs8 ? (col >> 3) * 16 + (col & 7) : col;
+        const int ucol = pairs8 ? gcol + 8 : width + col;
+        const float g = to_f32<T>(gate_up[row * 2 * width + gcol]);
+        const float u = to_f32<T>(gate_up[row * 2 * width + ucol]);
         const float act = round_to<T>(g / (1.0f + expf(-g)));
         out[i] = from_f32<T>(act * u);
     }
@@ -84,15 +88,17 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 
 // 8 bf16 values per thread when the width allows 16-byte accesses.
 __global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out,
-                                       int width, size_t total_vec) {
+                                       int width, size_t total_vec, int pairs8) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const int vec_per_row = width / 8;
     for (; i < total_vec; i += stride) {
         const size_t row = i / vec_per_row;
         const int col = (int)(i - row * vec_per_row) * 8;
-        const uint4 g4 = *reinterpret_cast<const uint4*>(gate_up + row * 2 * width + col);
-        const uint4 u4 = *reinterpret_cast<const uint4*>(gate_up + row * 2 * width + width + col);
+        const int gcol = pairs8 ? 2 * col : col;
+        const int ucol = pairs8 ? 2 * col + 8 : width + col;
+        const uint4 g4 = *reinterpret_cast<const uint4*>(gate_up + row * 2 * width + gcol);
+        const uint4 u4 = *reinterpret_cast<const uint4*>(gate_up + row * 2 * width + ucol);
         const bf16* g = reinterpret_cast<const bf16*>(&g4);
         const bf16* u = reinterpret_cast<const bf16*>(&u4);
         uint4 o4;
@@ -108,19 +114,20 @@ __global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gate_up, bf16* _
 }
 
 extern "C" int qil_silu_mul(const void* gate_up, void* out, int n_rows, int width, int act_dtype,
-                            cudaStream_t stream) {
+                            int pairs8, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width <= 0) QIL_REFUSE("silu_mul: width %d", width);
+    if (pairs8 && width % 8) QIL_REFUSE("silu_mul: the paired layout needs a width that is a multiple of 8, got %d", width);
     const size_t total = (size_t)n_rows * width;
     if (act_dtype == QIL_BF16 && width % 8 == 0 && ((uintptr_t)gate_up % 16) == 0 && ((uintptr_t)out % 16) == 0) {
         const size_t total_vec = total / 8;
         const int blocks = (int)((total_vec + 255) / 256 < 148 * 16 ? (total_vec + 255) / 256 : 148 * 16);
-        silu_mul_bf16x8_kernel<<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, width, total_vec);
+        silu_mul_bf16x8_kernel<<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, width, total_vec, pairs8);
         QIL_CHECK_LAUNCH();
     }
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     QIL_DISPATCH_1(act_dtype,
-        silu_mul_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, width, total));
+        silu_mul_kernel<T><<<blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, width, total, pairs8));
     QIL_CHECK_LAUNCH();
 }
 

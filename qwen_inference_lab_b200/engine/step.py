@@ -102,16 +102,19 @@ class StepRunner:
         positions = np.arange(n) - seg_start[seg_of_token] + starts[seg_of_token]
         token_row = rows[seg_of_token]
         logit_rows = np.array([seg_start[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int64)
-        tile_seg, tile_off = [], []
-        for i in np.nonzero(lens > 1)[0]:
-            for off in range(0, int(lens[i]), QUERY_TILE):
-                tile_seg.append(i)
-                tile_off.append(off)
-        decode_seg = np.nonzero(lens == 1)[0]
+        # query tiles of segments longer than one token: (first token, its position, rows, block-table row)
+        tiles = [(seg_start[i] + off, starts[i] + off, min(QUERY_TILE, int(lens[i]) - off), rows[i])
+                 for i in np.nonzero(lens > 1)[0] for off in range(0, int(lens[i]), QUERY_TILE)]
+        # the longest tiles of the longest contexts first: they take longest, the short ones fill the gaps
+        tiles.sort(key=lambda t: -(t[1] + t[2]))
+        tile_info = np.array(tiles, dtype=np.int64).reshape(-1)
+        # single-token segments: (token, its position, block-table row, 0)
+        single = np.nonzero(lens == 1)[0]
+        decode_info = np.stack([seg_start[single], starts[single], rows[single], np.zeros_like(single)],
+                               axis=1).reshape(-1) if len(single) else np.zeros(0, dtype=np.int64)
         sections = [("token_ids", token_ids), ("positions", positions), ("token_row", token_row),
                     ("seg_row", rows), ("seg_start", seg_start), ("seg_len", lens), ("seg_pos0", starts),
-                    ("logit_rows", logit_rows), ("tile_seg", np.array(tile_seg, dtype=np.int64)),
-                    ("tile_off", np.array(tile_off, dtype=np.int64)), ("decode_seg", decode_seg)]
+                    ("logit_rows", logit_rows), ("tile_info", tile_info), ("decode_info", decode_info)]
         offsets, total = {}, 0
         for name, values in sections:
             offsets[name] = (total, len(values))
@@ -131,8 +134,8 @@ class StepRunner:
             n_tokens=n, n_segments=s, dtype=self.model.dtype, device=self.device,
             token_ids=section("token_ids"), positions=section("positions"), token_row=section("token_row"),
             seg_row=section("seg_row"), seg_start=section("seg_start"), seg_len=section("seg_len"),
-            seg_pos0=section("seg_pos0"), n_tiles=offsets["tile_seg"][1], tile_seg=section("tile_seg"),
-            tile_off=section("tile_off"), n_decode=offsets["decode_seg"][1], decode_seg=section("decode_seg"),
+            seg_pos0=section("seg_pos0"), n_tiles=offsets["tile_info"][1] // 4, tile_info=section("tile_info"),
+            n_decode=offsets["decode_info"][1] // 4, decode_info=section("decode_info"),
             max_context=max_context, h_seg_row=host["seg_row"], h_seg_start=host["seg_start"],
             h_seg_len=host["seg_len"], h_seg_pos0=host["seg_pos0"])
 
@@ -162,7 +165,7 @@ class StepRunner:
         packed, offsets, host, n, s, max_context = self._describe(entries)
         self.cache.flush_tables()
         self._upload(packed)
-        all_single = offsets["tile_seg"][1] == 0 and offsets["logit_rows"][1] == n \
+        all_single = offsets["tile_info"][1] == 0 and offsets["logit_rows"][1] == n \
             and all(e.want == [0] for e in entries)
         if self.use_graphs and all_single and n <= self.graph_max_batch:
             logits = self._run_graph(offsets, host, n, s, max_context)

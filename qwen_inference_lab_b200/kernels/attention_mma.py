@@ -15,7 +15,8 @@ from . import build
 from .ops import KernelError, _check, _p, _stream
 
 _libs: dict = {}
-DECODE_SPAN = 256
+KV_TILE = 64
+MAX_DECODE_SPAN = 2048
 
 
 def supports(head_dim, n_q_heads, n_kv_heads) -> bool:
@@ -28,10 +29,25 @@ def library(head_dim):
         if not supports(head_dim, 1, 1):
             raise KernelError(f"the tensor-core attention takes head sizes 16, 32, ..., 256, not {head_dim}")
         lib = build.load(f"qil_attn_d{head_dim}", ["attention_mma.cu"], {"QIL_HEAD_DIM": head_dim})
-        if lib.qil_attn_head_dim() != head_dim or lib.qil_attn_decode_span() != DECODE_SPAN:
+        if lib.qil_attn_head_dim() != head_dim or lib.qil_attn_max_decode_span() != MAX_DECODE_SPAN:
             raise KernelError("attention library was built for other constants")
         _libs[head_dim] = lib
     return lib
+
+
+def choose_span(n_decode, n_q_heads, n_kv_heads, max_context) -> int:
+    """Positions per block of the single-token kernel.
+
+    A block's start-up (its metadata, page ids and first tile arrive one after the other) is worth
+    several tiles of streaming, so spans are at least 512 positions; with many tokens decoding they grow
+    to 2048 so that there are not many more blocks than the GPU holds at once (measured on B200:
+    batch 1 and 8 at context 8192 are fastest at 512, batch 64 at 2048).
+    """
+    blocks_per_span = n_decode * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16)
+    span = 512
+    while span < MAX_DECODE_SPAN and blocks_per_span * ((max_context + span - 1) // span) > 2048:
+        span *= 2
+    return span
 
 
 def decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim):
@@ -45,24 +61,25 @@ def decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim):
     return scratch
 
 
-def prefill(q, pages, out, tile_seg, tile_off, n_tiles, seg_start, seg_len, seg_pos0, seg_row, block_table,
-            n_q_heads, n_kv_heads, head_dim, page_size, window, scale):
+def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, head_dim, page_size, window,
+            scale):
+    """tile_info int32 [n_tiles * 4]: (first token, its position, rows <= 64, block-table row) per tile."""
     lib = library(head_dim)
     _check(lib, lib.qil_attn_prefill(
-        _p(q), _p(pages), _p(out), _p(tile_seg), _p(tile_off), c_int(n_tiles), _p(seg_start), _p(seg_len),
-        _p(seg_pos0), _p(seg_row), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads),
-        c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), _stream()),
-        "attention (prompt portions)")
+        _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), _p(block_table), c_int(block_table.shape[1]),
+        c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window),
+        c_float(scale), _stream()), "attention (prompt portions)")
 
 
-def decode(q, pages, out, decode_seg, n_decode, part_o, part_ml, n_spans, seg_start, seg_len, seg_pos0, seg_row,
-           block_table, n_q_heads, n_kv_heads, head_dim, page_size, window, scale):
+def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
+           n_q_heads, n_kv_heads, head_dim, page_size, window, scale):
+    """decode_info int32 [n_decode * 4]: (token, its position, block-table row, 0) per single token."""
     lib = library(head_dim)
     _check(lib, lib.qil_attn_decode(
-        _p(q), _p(pages), _p(out), _p(decode_seg), c_int(n_decode), _p(part_o), _p(part_ml), c_int(n_spans),
-        _p(seg_start), _p(seg_len), _p(seg_pos0), _p(seg_row), _p(block_table), c_int(block_table.shape[1]),
-        c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window),
-        c_float(scale), _stream()), "attention (single tokens)", kernels=2)
+        _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), c_int(n_spans),
+        c_int(span_len), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads),
+        c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), _stream()),
+        "attention (single tokens)", kernels=2)
 
 
 def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
@@ -72,12 +89,11 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
     if tuple(cache.pages.shape[1:]) != (2, n_kv_heads, cache.page_size, head_dim):
         raise KernelError(f"attention: cache layout {tuple(cache.pages.shape)}")
     if ctx.n_tiles:
-        prefill(q, cache.pages, out, ctx.tile_seg, ctx.tile_off, ctx.n_tiles, ctx.seg_start, ctx.seg_len,
-                ctx.seg_pos0, ctx.seg_row, cache.block_table, n_q_heads, n_kv_heads, head_dim,
-                cache.page_size, window, scale)
+        prefill(q, cache.pages, out, ctx.tile_info, ctx.n_tiles, cache.block_table, n_q_heads, n_kv_heads,
+                head_dim, cache.page_size, window, scale)
     if ctx.n_decode:
-        n_spans = max(1, (ctx.max_context + DECODE_SPAN - 1) // DECODE_SPAN)
+        span_len = choose_span(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context)
+        n_spans = max(1, (ctx.max_context + span_len - 1) // span_len)
         part_o, part_ml = decode_scratch(ctx, ctx.n_decode, n_q_heads, n_spans, head_dim)
-        decode(q, cache.pages, out, ctx.decode_seg, ctx.n_decode, part_o, part_ml, n_spans, ctx.seg_start,
-               ctx.seg_len, ctx.seg_pos0, ctx.seg_row, cache.block_table, n_q_heads, n_kv_heads, head_dim,
-               cache.page_size, window, scale)
+        decode(q, cache.pages, out, ctx.decode_info, ctx.n_decode, part_o, part_ml, n_spans, span_len,
+               cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale)

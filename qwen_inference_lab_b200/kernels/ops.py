@@ -16,7 +16,9 @@ from . import build
 F32, BF16 = 0, 1
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 
-CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "attention_generic.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "gemm_small_m.cu", "attention_generic.cu",
+                "sampling.cu"]
+SMALL_M_MAX_ROWS = 16
 
 _core = None
 
@@ -106,8 +108,9 @@ def rmsnorm(x, weight, eps, out=None, rows=None):
     return out
 
 
-def silu_mul(gate_up, out=None):
-    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+def silu_mul(gate_up, out=None, pairs8=False):
+    """out = silu(gate) * up.  gate_up holds the gate columns then the up columns, or with
+    ``pairs8`` groups of 16 columns: 8 gate columns followed by their 8 up columns."""
     _need(gate_up, "gate_up", ndim=2)
     if gate_up.shape[1] % 2:
         raise KernelError("silu_mul: the input's width must be even (gate columns then up columns)")
@@ -117,7 +120,45 @@ def silu_mul(gate_up, out=None):
     _need(out, "out", gate_up.dtype, 2)
     lib = core()
     _check(lib, lib.qil_silu_mul(_p(gate_up), _p(out), c_int(gate_up.shape[0]), c_int(width),
-                                 c_int(dtype_code(gate_up.dtype)), _stream()), "silu_mul")
+                                 c_int(dtype_code(gate_up.dtype)), c_int(1 if pairs8 else 0), _stream()), "silu_mul")
+    return out
+
+
+def small_m_ok(a, weight) -> bool:
+    """Can ``gemm_small_m`` take this product?  bfloat16, at most 16 rows, K a multiple of 8."""
+    return (a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and a.shape[0] <= SMALL_M_MAX_ROWS
+            and weight.shape[1] % 8 == 0 and a.is_contiguous())
+
+
+def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=False, silu_pairs=False):
+    """out = a @ weight.T (+ bias) (+ residual) for a decode step's few rows, streaming the weight once.
+
+    a bfloat16 [M <= 16, K]; weight bfloat16 [N, K].  ``out_float32`` returns float32 (the LM head).
+    ``silu_pairs``: weight rows are groups of [8 gate, 8 up]; returns silu(gate) * up, bfloat16 [M, N/2].
+    ``residual`` may be ``out`` itself.
+    """
+    _need(a, "a", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
+    m, k = a.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"gemm_small_m: a {tuple(a.shape)} against weight {tuple(weight.shape)}")
+    out_shape = (m, n // 2) if silu_pairs else (m, n)
+    out_dtype = torch.float32 if out_float32 else torch.bfloat16
+    if bias is not None:
+        _need(bias, "bias", torch.bfloat16, 1)
+    if residual is not None:
+        _need(residual, "residual", torch.bfloat16, 2)
+        if residual.shape != out_shape:
+            raise KernelError("gemm_small_m: residual has the wrong shape")
+    if out is None:
+        out = torch.empty(out_shape, dtype=out_dtype, device=a.device)
+    _need(out, "out", out_dtype, 2)
+    if out.shape != out_shape:
+        raise KernelError("gemm_small_m: out has the wrong shape")
+    lib = core()
+    _check(lib, lib.qil_gemm_small_m(_p(a), _p(weight), _p(bias), _p(residual), _p(out), c_int(m), c_int(n), c_int(k),
+                                     c_int(1 if out_float32 else 0), c_int(1 if silu_pairs else 0), _stream()),
+           "gemm_small_m")
     return out
 
 

@@ -140,13 +140,13 @@ class StepContext:
     seg_start: torch.Tensor          # [S] first token of the segment in the flat batch
     seg_len: torch.Tensor            # [S]
     seg_pos0: torch.Tensor           # [S] position of the segment's first token
-    # query tiles of segments longer than one token: (segment, offset inside it)
+    # query tiles (64 tokens) of segments longer than one token:
+    # 4 ints each = (first token in the flat batch, its absolute position, rows in the tile, block-table row)
     n_tiles: int
-    tile_seg: torch.Tensor           # [n_tiles]
-    tile_off: torch.Tensor           # [n_tiles]
-    # segments of exactly one token (decode rows)
+    tile_info: torch.Tensor          # [n_tiles * 4]
+    # segments of exactly one token (decode rows): 4 ints each = (token, its position, block-table row, 0)
     n_decode: int
-    decode_seg: torch.Tensor         # [n_decode]
+    decode_info: torch.Tensor        # [n_decode * 4]
     max_context: int                 # largest start+len over the batch's segments (host upper bound)
     h_seg_row: object = None
     h_seg_start: object = None

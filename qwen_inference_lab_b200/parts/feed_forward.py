@@ -5,6 +5,8 @@ activation dtype before the multiply, as elementwise tensor code does.
 """
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
 from .base import FeedForward
 from .linear import Linear, StackedLinear
@@ -20,10 +22,26 @@ class GatedMLP(FeedForward):
                                                    (names["up"], intermediate_size)])
         self.down = Linear(intermediate_size, hidden_size, name=names["down"])
 
+        self.pairs8 = False
+
     def children(self):
         return [self.gate_up, self.down]
 
+    def finalize(self, device, dtype):
+        super().finalize(device, dtype)
+        w = self.gate_up._w
+        inner = self.intermediate_size
+        if w.dtype == torch.bfloat16 and inner % 8 == 0 and self.hidden_size % 8 == 0:
+            # rows as groups of [8 gate, 8 up]: a block of the decode GEMM then holds matching gate and up
+            # features and applies the activation in its epilogue
+            self.gate_up._w = w.view(2, inner // 8, 8, self.hidden_size).transpose(0, 1).reshape(
+                2 * inner, self.hidden_size).contiguous()
+            self.pairs8 = True
+
     def forward(self, ctx, x, residual=None):
-        gate_up = self.gate_up.forward(ctx, x)
-        hidden = ops.silu_mul(gate_up)
+        if self.pairs8 and ops.small_m_ok(x, self.gate_up._w):
+            hidden = ops.gemm_small_m(x, self.gate_up._w, silu_pairs=True)
+        else:
+            gate_up = self.gate_up.forward(ctx, x)
+            hidden = ops.silu_mul(gate_up, pairs8=self.pairs8)
         return self.down.forward(ctx, hidden, residual=residual)

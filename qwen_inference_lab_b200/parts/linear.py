@@ -5,7 +5,9 @@ Weights are row-major ``[out_features, in_features]`` as the reference's
 activations goes to the library GEMM, which is what the reference's engine uses
 for its projections (qil/model.py:52-54,69-71: ``nn.Linear`` -> cuBLAS); every
 other combination (the true 32-bit path, or a weight stored in float32 inside a
-bfloat16 model) runs the engine's own float32 CUDA-core product.
+bfloat16 model) runs the engine's own float32 CUDA-core product.  Products of at
+most 16 rows (decode steps) run the engine's own weight-streaming kernel instead
+of the library.
 """
 from __future__ import annotations
 
@@ -55,6 +57,9 @@ class Linear(Part):
     def forward(self, ctx, x, residual=None, out=None, out_float32=False):
         """``x`` [N, in] -> [N, out]; adds ``residual`` [N, out] when given (may be ``out``)."""
         weight, bias = self._weight(), self._bias()
+        if ops.small_m_ok(x, weight):
+            # a decode step's few rows: the engine's weight-streaming kernel
+            return ops.gemm_small_m(x, weight, bias=bias, residual=residual, out=out, out_float32=out_float32)
         if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
             if out_float32:
                 result = _library_mm_f32_out(x, weight)

@@ -209,31 +209,29 @@ def test_attention_generic(dtype, case):
     close(out, expected, dtype, scale=2)
 
 
-def run_mma(q, pool, table, meta, n_q, n_kv, d, page, window):
+def run_mma(q, pool, table, meta, n_q, n_kv, d, page, window, span_len=256):
     from qwen_inference_lab_b200.kernels import attention_mma
     as_int = lambda values: torch.tensor(values, dtype=torch.int32).cuda()
-    tile_seg, tile_off, decode_seg = [], [], []
-    for s, length in enumerate(meta["seg_len"]):
+    tile_info, decode_info = [], []
+    for start, length, pos0, row in zip(meta["seg_start"], meta["seg_len"], meta["seg_pos0"], meta["seg_row"]):
         if length == 1:
-            decode_seg.append(s)
+            decode_info += [start, pos0, row, 0]
         else:
             for off in range(0, length, 64):
-                tile_seg.append(s)
-                tile_off.append(off)
+                tile_info += [start + off, pos0 + off, min(64, length - off), row]
     out = torch.full(q.shape, float("nan"), dtype=q.dtype).cuda()
-    args = (as_int(meta["seg_start"]), as_int(meta["seg_len"]), as_int(meta["seg_pos0"]), as_int(meta["seg_row"]),
-            table.cuda())
     qg, pg = q.cuda(), pool.cuda()
-    if tile_seg:
-        attention_mma.prefill(qg, pg, out, as_int(tile_seg), as_int(tile_off), len(tile_seg), *args,
+    if tile_info:
+        attention_mma.prefill(qg, pg, out, as_int(tile_info), len(tile_info) // 4, table.cuda(),
                               n_q, n_kv, d, page, window, d ** -0.5)
-    if decode_seg:
+    if decode_info:
+        n_decode = len(decode_info) // 4
         longest = max(p0 + n for p0, n in zip(meta["seg_pos0"], meta["seg_len"]))
-        n_spans = (longest + attention_mma.DECODE_SPAN - 1) // attention_mma.DECODE_SPAN + 1   # one spare span
-        part_o = torch.full((len(decode_seg) * n_q * n_spans * d,), float("nan"), dtype=torch.float32).cuda()
-        part_ml = torch.full((len(decode_seg) * n_q * n_spans * 2,), float("nan"), dtype=torch.float32).cuda()
-        attention_mma.decode(qg, pg, out, as_int(decode_seg), len(decode_seg), part_o, part_ml, n_spans, *args,
-                             n_q, n_kv, d, page, window, d ** -0.5)
+        n_spans = (longest + span_len - 1) // span_len + 1   # one spare span
+        part_o = torch.full((n_decode * n_q * n_spans * d,), float("nan"), dtype=torch.float32).cuda()
+        part_ml = torch.full((n_decode * n_q * n_spans * 2,), float("nan"), dtype=torch.float32).cuda()
+        attention_mma.decode(qg, pg, out, as_int(decode_info), n_decode, part_o, part_ml, n_spans, span_len,
+                             table.cuda(), n_q, n_kv, d, page, window, d ** -0.5)
     return out
 
 
@@ -256,8 +254,18 @@ def test_attention_tensor_core(case):
     last_meta = dict(seg_start=list(range(len(lengths))), seg_len=[1] * len(lengths),
                      seg_pos0=[n - 1 for n in lengths], seg_row=meta["seg_row"])
     last_expected = torch.stack([expected[s + n - 1] for s, n in zip(meta["seg_start"], meta["seg_len"])])
-    out = run_mma(last_q, pool, table, last_meta, n_q, n_kv, d, page, window)
-    close(out, last_expected, torch.bfloat16, scale=2)
+    for span_len in (64, 256, 2048):
+        out = run_mma(last_q, pool, table, last_meta, n_q, n_kv, d, page, window, span_len=span_len)
+        close(out, last_expected, torch.bfloat16, scale=2)
+
+
+def test_span_choice_fills_the_gpu_and_stays_legal():
+    from qwen_inference_lab_b200.kernels import attention_mma
+    for n_decode, ctx in ((1, 8192), (8, 8192), (64, 8192), (1, 100), (256, 40000), (3, 1)):
+        span = attention_mma.choose_span(n_decode, 32, 8, ctx)
+        assert span % 64 == 0 and 64 <= span <= attention_mma.MAX_DECODE_SPAN
+    assert attention_mma.choose_span(1, 32, 8, 8192) < attention_mma.choose_span(64, 32, 8, 8192)
+    assert attention_mma.choose_span(8, 32, 8, 8192) == 512
 
 
 @pytest.mark.parametrize("form", ["portion", "single"])
@@ -311,3 +319,46 @@ def test_sample_rows_temperature_matches_plain_and_is_batch_independent():
     freq = torch.bincount(drawn.cpu().long(), minlength=4).float() / 4000
     want = torch.softmax(small[0] / 0.7, dim=0)
     assert (freq - want).abs().max() < 0.03
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 16, 8), (3, 200, 96), (8, 129, 136), (9, 64, 4096), (16, 1000, 520)])
+def test_gemm_small_m(m, n, k):
+    torch.manual_seed(9)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    w = (torch.randn(n, k) * 0.1).to(torch.bfloat16)
+    bias = (torch.randn(n) * 0.1).to(torch.bfloat16)
+    residual = torch.randn(m, n).to(torch.bfloat16)
+    product = a.double() @ w.double().t()
+    close(ops().gemm_small_m(a.cuda(), w.cuda()), product.float(), torch.bfloat16, scale=4)
+    close(ops().gemm_small_m(a.cuda(), w.cuda(), bias=bias.cuda(), residual=residual.cuda()),
+          (product + bias.double() + residual.double()).float(), torch.bfloat16, scale=4)
+    exact = ops().gemm_small_m(a.cuda(), w.cuda(), out_float32=True)
+    assert exact.dtype == torch.float32
+    torch.testing.assert_close(exact.cpu(), product.float(), atol=1e-4, rtol=1e-4)
+    # in place on the residual, and a row's result does not depend on the other rows
+    buffer = residual.cuda().clone()
+    ops().gemm_small_m(a.cuda(), w.cuda(), residual=buffer, out=buffer)
+    close(buffer, (product + residual.double()).float(), torch.bfloat16, scale=4)
+    alone = ops().gemm_small_m(a[-1:].cuda().contiguous(), w.cuda(), out_float32=True)
+    assert torch.equal(alone.cpu()[0], exact.cpu()[-1])
+
+
+@pytest.mark.parametrize("m,inner,k", [(1, 8, 16), (5, 200, 96), (16, 1024, 256)])
+def test_gemm_small_m_with_gate_epilogue_and_paired_silu(m, inner, k):
+    torch.manual_seed(10)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    gate_w = (torch.randn(inner, k) * 0.2).to(torch.bfloat16)
+    up_w = (torch.randn(inner, k) * 0.2).to(torch.bfloat16)
+    gate = (a.float() @ gate_w.float().t()).to(torch.bfloat16)
+    up = (a.float() @ up_w.float().t()).to(torch.bfloat16)
+    expected = torch.nn.functional.silu(gate) * up
+    paired = torch.cat([gate_w, up_w]).view(2, inner // 8, 8, k).transpose(0, 1).reshape(2 * inner, k).contiguous()
+    fused = ops().gemm_small_m(a.cuda(), paired.cuda(), silu_pairs=True)
+    assert fused.shape == (m, inner)
+    close(fused, expected, torch.bfloat16, scale=2)
+    # the stand-alone activation kernel reads the same paired layout (prompt portions use it after the library GEMM)
+    paired_columns = torch.cat([gate, up], dim=1).view(m, 2, inner // 8, 8).transpose(1, 2).reshape(m, 2 * inner)
+    separate = ops().silu_mul(paired_columns.contiguous().cuda(), pairs8=True)
+    assert torch.equal(separate.cpu(), expected)
+    close(ops().silu_mul(paired_columns.float().contiguous().cuda(), pairs8=True),
+          torch.nn.functional.silu(gate.float()) * up.float(), torch.float32, scale=2)

@@ -27,16 +27,15 @@ def load_library():
     return lib
 
 
-def decode_case(lengths, n_q, n_kv, page, seed):
+def decode_case(lengths, n_q, n_kv, page, seed, span_len=256):
     """The last token of each request attends over its paged history (built as in the kernel tests)."""
     from tests.test_kernels_gpu import attention_case
     starts = [n - 1 for n in lengths]
     q, pool, table, meta, expected = attention_case(n_q, n_kv, HEAD_DIM, lengths, starts, torch.bfloat16, page, seed)
-    as_int = lambda values: torch.tensor(values, dtype=torch.int32).cuda()
+    info = [v for token, (pos, row) in enumerate(zip(meta["seg_pos0"], meta["seg_row"])) for v in (token, pos, row, 0)]
     return dict(q=q.cuda(), pool=pool.cuda(), table=table.cuda(), expected=expected, n_q=n_q, n_kv=n_kv, page=page,
-                decode_seg=as_int(list(range(len(lengths)))), seg_start=as_int(meta["seg_start"]),
-                seg_len=as_int(meta["seg_len"]), seg_pos0=as_int(meta["seg_pos0"]), seg_row=as_int(meta["seg_row"]),
-                n_spans=(max(lengths) + 255) // 256)
+                decode_info=torch.tensor(info, dtype=torch.int32).cuda(), span_len=span_len,
+                n_spans=(max(lengths) + span_len - 1) // span_len)
 
 
 def regular(case):
@@ -46,9 +45,9 @@ def regular(case):
     slots = n * case["n_q"] * case["n_spans"]
     part_o = torch.empty(slots * HEAD_DIM, dtype=torch.float32, device="cuda")
     part_ml = torch.empty(slots * 2, dtype=torch.float32, device="cuda")
-    attention_mma.decode(case["q"], case["pool"], out, case["decode_seg"], n, part_o, part_ml, case["n_spans"],
-                         case["seg_start"], case["seg_len"], case["seg_pos0"], case["seg_row"], case["table"],
-                         case["n_q"], case["n_kv"], HEAD_DIM, case["page"], 0, HEAD_DIM ** -0.5)
+    attention_mma.decode(case["q"], case["pool"], out, case["decode_info"], n, part_o, part_ml, case["n_spans"],
+                         case["span_len"], case["table"], case["n_q"], case["n_kv"], HEAD_DIM, case["page"], 0,
+                         HEAD_DIM ** -0.5)
     return out
 
 
@@ -57,10 +56,10 @@ def no_alloc(lib, case, n_spans=None):
     out = torch.full_like(case["q"], float("nan"))
     ptr = lambda t: c_void_p(t.data_ptr())
     code = lib.qil_attn_decode_noalloc(
-        ptr(case["q"]), ptr(case["pool"]), ptr(out), ptr(case["decode_seg"]), c_int(n),
-        c_int(n_spans or case["n_spans"]), ptr(case["seg_start"]), ptr(case["seg_len"]), ptr(case["seg_pos0"]),
-        ptr(case["seg_row"]), ptr(case["table"]), c_int(case["table"].shape[1]), c_int(case["n_q"]), c_int(case["n_kv"]),
-        c_int(case["page"]), c_int(case["pool"].shape[0]), c_int(0), c_float(HEAD_DIM ** -0.5),
+        ptr(case["q"]), ptr(case["pool"]), ptr(out), ptr(case["decode_info"]), c_int(n),
+        c_int(n_spans or case["n_spans"]), c_int(case["span_len"]), ptr(case["table"]),
+        c_int(case["table"].shape[1]), c_int(case["n_q"]), c_int(case["n_kv"]), c_int(case["page"]),
+        c_int(case["pool"].shape[0]), c_int(0), c_float(HEAD_DIM ** -0.5),
         c_void_p(torch.cuda.current_stream().cuda_stream))
     return code, out
 
@@ -69,7 +68,7 @@ def test_no_alloc_entry_point_matches_the_regular_one_twice_in_a_row():
     lib = load_library()
     assert lib.qil_attn_decode_noalloc_max_floats() == 4 * 1024 * 1024
     first = decode_case([700, 33, 257, 1], n_q=8, n_kv=2, page=16, seed=40)
-    second = decode_case([90, 1300], n_q=4, n_kv=4, page=8, seed=41)      # other sizes: stale scratch must not matter
+    second = decode_case([90, 1300], n_q=4, n_kv=4, page=8, seed=41, span_len=512)   # other sizes: stale scratch must not matter
     allocated_before = torch.cuda.memory_allocated()
     for case in (first, second):
         want = regular(case)
