@@ -445,17 +445,29 @@ attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, con
     int s_hi = pos / span_len;
     if (s_hi >= n_spans) s_hi = n_spans - 1;   // cannot happen when the host sized n_spans for the batch
     const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
+    // every thread reads the few (max, sum) pairs itself: the loads are independent and overlap
     float mx = -INFINITY;
     for (int s = s_lo; s <= s_hi; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
     const float ms = (mx == -INFINITY) ? 0.f : mx;
     float sum = 0.f;
-    for (int s = s_lo; s <= s_hi; ++s) sum += exp2f(part_ml[(base + s) * 2] - ms) * part_ml[(base + s) * 2 + 1];
+    float acc[(D + 127) / 128];
+#pragma unroll
+    for (int i = 0; i < (D + 127) / 128; ++i) acc[i] = 0.f;
+#pragma unroll 4
+    for (int s = s_lo; s <= s_hi; ++s) {
+        const float f = exp2f(part_ml[(base + s) * 2] - ms);
+        sum += f * part_ml[(base + s) * 2 + 1];
+#pragma unroll
+        for (int i = 0; i < (D + 127) / 128; ++i) {
+            const int col = threadIdx.x + i * 128;
+            if (col < D) acc[i] += f * part_o[(base + s) * D + col];
+        }
+    }
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
-    for (int col = threadIdx.x; col < D; col += 128) {
-        float acc = 0.f;
-        for (int s = s_lo; s <= s_hi; ++s)
-            acc += exp2f(part_ml[(base + s) * 2] - ms) * part_o[(base + s) * D + col];
-        p.out[((size_t)n * p.n_q_heads + head) * D + col] = __float2bfloat16_rn(acc * inv);
+#pragma unroll
+    for (int i = 0; i < (D + 127) / 128; ++i) {
+        const int col = threadIdx.x + i * 128;
+        if (col < D) p.out[((size_t)n * p.n_q_heads + head) * D + col] = __float2bfloat16_rn(acc[i] * inv);
     }
 }
 

@@ -22,10 +22,26 @@ __global__ void embed_gather_kernel(const W* __restrict__ table, const int* __re
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<T>(to_f32<W>(src[i]));
 }
 
+// bfloat16 table and output with a width that allows 16-byte copies
+__global__ void embed_gather_bf16x8_kernel(const bf16* __restrict__ table, const int* __restrict__ ids,
+                                           bf16* __restrict__ out, int width, int vocab) {
+    const int row = blockIdx.x;
+    int id = ids[row];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * width);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * width);
+    for (int i = threadIdx.x; i < width / 8; i += blockDim.x) dst[i] = src[i];
+}
+
 extern "C" int qil_embed_gather(const void* table, int table_dtype, const int* ids, void* out,
                                 int out_dtype, int n_rows, int width, int vocab, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width <= 0 || vocab <= 0) QIL_REFUSE("embed_gather: width %d vocab %d", width, vocab);
+    if (out_dtype == QIL_BF16 && table_dtype == QIL_BF16 && width % 8 == 0 &&
+        (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
+        embed_gather_bf16x8_kernel<<<n_rows, 128, 0, stream>>>((const bf16*)table, ids, (bf16*)out, width, vocab);
+        QIL_CHECK_LAUNCH();
+    }
     QIL_DISPATCH_2(out_dtype, table_dtype,
         embed_gather_kernel<T, W><<<n_rows, 256, 0, stream>>>((const W*)table, ids, (T*)out, width, vocab));
     QIL_CHECK_LAUNCH();
@@ -55,11 +71,64 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const W* __restrict__ we
     }
 }
 
+// bfloat16 rows of up to 256 * 8 * RMS_VPT elements: the whole row sits in registers, every load is
+// 16 bytes wide and issued before the first use, so a row costs one memory round trip, not one per element.
+#define RMS_VPT 4
+template <typename W>
+__global__ void __launch_bounds__(256)
+rmsnorm_bf16x8_kernel(const bf16* __restrict__ x, const W* __restrict__ weight, const int* __restrict__ rows,
+                      bf16* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src_row = rows ? rows[r] : r;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)src_row * width);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)r * width);
+    const int vectors = width / 8;
+    uint4 v[RMS_VPT];
+#pragma unroll
+    for (int i = 0; i < RMS_VPT; ++i) {
+        const int idx = threadIdx.x + i * 256;
+        v[i] = idx < vectors ? src[idx] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < RMS_VPT; ++i) {
+        const bf16* e = reinterpret_cast<const bf16*>(&v[i]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { const float f = __bfloat162float(e[k]); sq += f * f; }
+    }
+    sq = block_sum(sq, scratch);
+    const float scale = 1.0f / sqrtf(sq / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < RMS_VPT; ++i) {
+        const int idx = threadIdx.x + i * 256;
+        if (idx >= vectors) continue;
+        const bf16* e = reinterpret_cast<const bf16*>(&v[i]);
+        uint4 o4;
+        bf16* o = reinterpret_cast<bf16*>(&o4);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float normed = round_to<bf16>(__bfloat162float(e[k]) * scale);
+            o[k] = __float2bfloat16_rn(normed * to_f32<W>(weight[idx * 8 + k]));
+        }
+        dst[idx] = o4;
+    }
+}
+
 extern "C" int qil_rmsnorm(const void* x, const void* weight, const int* rows, void* out,
                            int n_rows, int width, float eps, int act_dtype, int weight_dtype,
                            cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width <= 0) QIL_REFUSE("rmsnorm: width %d", width);
+    if (act_dtype == QIL_BF16 && width % 8 == 0 && width <= 256 * 8 * RMS_VPT &&
+        (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        if (weight_dtype == QIL_BF16)
+            rmsnorm_bf16x8_kernel<bf16><<<n_rows, 256, 0, stream>>>((const bf16*)x, (const bf16*)weight, rows, (bf16*)out, width, eps);
+        else if (weight_dtype == QIL_F32)
+            rmsnorm_bf16x8_kernel<float><<<n_rows, 256, 0, stream>>>((const bf16*)x, (const float*)weight, rows, (bf16*)out, width, eps);
+        else QIL_REFUSE("unknown dtype code %d", weight_dtype);
+        QIL_CHECK_LAUNCH();
+    }
     QIL_DISPATCH_2(act_dtype, weight_dtype,
         rmsnorm_kernel<T, W><<<n_rows, 256, 0, stream>>>((const T*)x, (const W*)weight, rows, (T*)out, width, eps));
     QIL_CHECK_LAUNCH();
