@@ -71,7 +71,7 @@ class Engine:
         entries, ready = [], []
         for work in plan:
             request = requests[work.request_id]
-            done = work.start + len(work.tokens) == len(request.input_tokens)
+            done = work.start + len(work.tokens) == request.input_length
             entries.append(StepEntry(work.request_id, work.tokens, [len(work.tokens) - 1] if done else []))
             if done:
                 ready.append(request)

@@ -43,6 +43,19 @@ class Request:
         return self.prompt + self.output
 
     @property
+    def input_length(self):
+        return len(self.prompt) + len(self.output)
+
+    def input_slice(self, start, count):
+        """``input_tokens[start:start + count]`` without building the whole list."""
+        split = len(self.prompt)
+        if start >= split:
+            return self.output[start - split:start - split + count]
+        if start + count <= split:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.output[:start + count - split]
+
+    @property
     def cache_limit(self):
         # the last generated token is returned without being fed back (qil/scheduler.py:24-27)
         return len(self.prompt) + self.max_new_tokens - 1
@@ -91,12 +104,11 @@ class Scheduler:
                 break
             request_id = self.active.popleft()
             request = self.requests[request_id]
-            inputs = request.input_tokens
             chunk = self.prefill_chunk if request.computed < len(request.prompt) else 1
-            count = min(chunk, remaining, len(inputs) - request.computed)
+            count = min(chunk, remaining, request.input_length - request.computed)
             if count <= 0:
                 raise RuntimeError("active request has no input to compute")
-            work.append(Work(request_id, request.computed, inputs[request.computed:request.computed + count]))
+            work.append(Work(request_id, request.computed, request.input_slice(request.computed, count)))
             remaining -= count
             self.active.append(request_id)
         if not work and self.waiting:

@@ -181,6 +181,13 @@ class StepRunner:
         return logits
 
     def _run_graph(self, offsets, host, n, s, max_context):
+        """Replay (after recording, the first time) the graphs of an all-single-token step.
+
+        A step is recorded as a chain of graphs, a few layers each, not as one: submitting a graph of
+        several hundred kernels takes the host most of a millisecond before the GPU sees any of it,
+        and a step cannot be submitted before the previous one's tokens are known.  With a chain the
+        GPU runs the first layers while the host submits the rest.
+        """
         bucket = 512
         while bucket < max_context:
             bucket *= 2
@@ -193,16 +200,34 @@ class StepRunner:
             # one eager run first: libraries set up their workspaces outside the recording
             self.model.forward(ctx, self.views, logit_rows)
             torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
+            graphs = []
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
             before = ops.launch_count()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                logits = self.model.forward(ctx, self.views, logit_rows)
-            record = (graph, logits, ops.launch_count() - before)
+            with torch.cuda.stream(stream):
+                current = torch.cuda.CUDAGraph()
+                current.capture_begin(pool=self._graph_pool)
+
+                def cut():
+                    nonlocal current
+                    current.capture_end()
+                    graphs.append(current)
+                    current = torch.cuda.CUDAGraph()
+                    current.capture_begin(pool=self._graph_pool)
+
+                try:
+                    logits = self.model.forward(ctx, self.views, logit_rows, checkpoint=cut)
+                finally:
+                    current.capture_end()
+                graphs.append(current)
+            torch.cuda.current_stream().wait_stream(stream)
+            record = (graphs, logits, ops.launch_count() - before)
             self._graphs[key] = record
             self.launches_per_graph[n] = record[2]
-        graph, logits, launches = record
-        graph.replay()
+        graphs, logits, launches = record
+        for graph in graphs:
+            graph.replay()
         self.kernel_launches += launches
         return logits

@@ -45,6 +45,8 @@ class TokenEmbedding(Part):
 
 
 class DecoderModel(Part):
+    graph_safe = True      # the model itself only walks its parts; they decide
+
     def __init__(self, *, config, embedding, layers, order, final_norm, head, max_positions):
         self.config = config
         self.embedding, self.layers, self.final_norm, self.head = embedding, list(layers), final_norm, head
@@ -77,14 +79,19 @@ class DecoderModel(Part):
         self.device, self.dtype = torch.device(device), dtype
         super().finalize(device, dtype)
 
-    def forward(self, ctx, cache_views, logit_rows):
+    def forward(self, ctx, cache_views, logit_rows, checkpoint=None, calls_per_checkpoint=12):
         """Run the batch through every call of the order; float32 logits [R, vocab] or None.
 
         ``cache_views[i]`` is the view for order[i] (its own cache, or the one it reads);
         ``logit_rows`` int32 [R] indexes the flat batch (None or empty: no logits).
+        ``checkpoint`` is called between groups of layer calls: whoever records the step into
+        CUDA graphs cuts there, so that the GPU starts on the first layers while the rest is
+        still being submitted.
         """
         x = self.embedding.forward(ctx, ctx.token_ids)
         for index, call in enumerate(self.order):
+            if checkpoint is not None and index and index % calls_per_checkpoint == 0:
+                checkpoint()
             x = self.layers[call.layer].forward(ctx, x, cache_views[index])
         if logit_rows is None or logit_rows.shape[0] == 0:
             return None

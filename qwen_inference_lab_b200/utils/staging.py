@@ -16,6 +16,7 @@ class PinnedRing:
         self.depth = depth
         self.buffers = [None] * depth
         self.events = [None] * depth
+        self._spare = [None] * depth      # one event per buffer, made once
         self.nbytes = int(nbytes)
         self.index = 0
 
@@ -31,7 +32,9 @@ class PinnedRing:
         return self.buffers[i]
 
     def commit(self) -> None:
-        event = torch.cuda.Event()
+        event = self._spare[self.index]
+        if event is None:
+            event = self._spare[self.index] = torch.cuda.Event()
         event.record()
         self.events[self.index] = event
         self.index = (self.index + 1) % self.depth

@@ -56,6 +56,9 @@ def test_greedy_generation_matches_plain(models, dtype, budget, chunk, pages, pa
         check_greedy(prompt, row["token_ids"], weights, cfg, dtype)
     assert engine.idle and engine.cache.free_pages() == pages
     engine.cache.check_invariants()
+    # steps made of single tokens are replayed from recorded graphs, cut into several pieces
+    assert engine.runner.use_graphs and engine.runner._graphs
+    assert all(len(record[0]) >= 1 for record in engine.runner._graphs.values())
 
 
 def test_temperature_sampling_matches_plain_and_is_reproducible(models):
