@@ -65,6 +65,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (about 2 ulp; -inf gives 0): the softmax stays in float32, only the
+// library routine's range handling is skipped.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -111,12 +118,14 @@ __device__ __forceinline__ void issue_kv_tile(const AttnParams& p, const int* ro
 }
 
 // ------------------------------------------------------------------ prompt portions
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, (QIL_HEAD_DIM <= 128) ? 3 : 1)
 attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [64][LDS]
-    bf16* sK = sQ + Q_TILE * LDS;                       // [2][64][LDS]
+    // [K stage 0][K stage 1][V stage 0][V stage 1]; when the queries live in registers (head sizes up to
+    // 128) their tile borrows K stage 1 until the fragments are loaded, else it has a region of its own
+    bf16* sK = reinterpret_cast<bf16*>(smem_raw);      // [2][64][LDS]
     bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
+    bf16* sQ = Q_IN_REGS ? sK + KV_TILE * LDS : sV + 2 * KV_TILE * LDS;   // [64][LDS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int head = blockIdx.y;
     const int kv_head = head / (p.n_q_heads / p.n_kv_heads);
@@ -144,11 +153,21 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
         row_off[0][tid] = kv_row_offset(p, table, 0, kv_head, first_tile * KV_TILE + tid, lo, hi);
         row_off[1][tid] = kv_row_offset(p, table, 0, kv_head, (first_tile + 1) * KV_TILE + tid, lo, hi);
     }
+    cp_async_commit();                 // group: the queries
     __syncthreads();
     issue_kv_tile(p, row_off[0], sK, sV, tid);
-    cp_async_commit();
+    cp_async_commit();                 // group: the first tile
 
     unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];
+    if (Q_IN_REGS) {
+        cp_async_wait<1>();            // the queries have landed (the first tile may still be under way)
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks)
+            ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+                        sQ + (warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + ks * 16 + (lane >> 4) * 8);
+        __syncthreads();               // K stage 1 is free for the second tile
+    }
     float o[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
@@ -166,12 +185,6 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
         // the row offsets of the tile after next go where this tile's were (everyone has used those)
         if (tile + 2 <= last_tile && tid < KV_TILE)
             row_off[buf][tid] = kv_row_offset(p, table, 0, kv_head, (tile + 2) * KV_TILE + tid, lo, hi);
-        if (Q_IN_REGS && tile == first_tile) {
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks)
-                ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
-                            sQ + (warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + ks * 16 + (lane >> 4) * 8);
-        }
         const bf16* tK = sK + buf * KV_TILE * LDS;
         const bf16* tV = sV + buf * KV_TILE * LDS;
 
@@ -196,18 +209,30 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
                 mma_bf16(s[2 * np + 1], a, b2, b3);
             }
         }
-        // scale, mask by absolute position, online softmax (float32)
+        // scale, mask by absolute position, online softmax (float32).  A tile that lies wholly at or before
+        // the first row's position and inside the last row's window needs no mask.
         float tmax_a = -INFINITY, tmax_b = -INFINITY;
+        const bool full = (tile + 1) * KV_TILE - 1 <= pos0 && (p.window == 0 || tile * KV_TILE > hi - p.window);
+        if (full) {
 #pragma unroll
-        for (int nt = 0; nt < KV_TILE / 8; ++nt) {
+            for (int nt = 0; nt < KV_TILE / 8; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = tile * KV_TILE + nt * 8 + (lane & 3) * 2 + (e & 1);
-                const int pos = (e < 2) ? pos_a : pos_b;
-                const bool ok = key <= pos && (p.window == 0 || key > pos - p.window);
-                const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
-                s[nt][e] = v;
-                if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
+                for (int e = 0; e < 4; ++e) s[nt][e] *= p.scale_log2;
+                tmax_a = fmaxf(tmax_a, fmaxf(s[nt][0], s[nt][1]));
+                tmax_b = fmaxf(tmax_b, fmaxf(s[nt][2], s[nt][3]));
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < KV_TILE / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = tile * KV_TILE + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int pos = (e < 2) ? pos_a : pos_b;
+                    const bool ok = key <= pos && (p.window == 0 || key > pos - p.window);
+                    const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
+                    s[nt][e] = v;
+                    if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
+                }
             }
         }
         tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 1));
@@ -216,13 +241,13 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
         tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 2));
         const float mn_a = fmaxf(m_a, tmax_a), mn_b = fmaxf(m_b, tmax_b);
         const float ms_a = (mn_a == -INFINITY) ? 0.f : mn_a, ms_b = (mn_b == -INFINITY) ? 0.f : mn_b;
-        const float corr_a = exp2f(m_a - ms_a), corr_b = exp2f(m_b - ms_b);
+        const float corr_a = fast_exp2(m_a - ms_a), corr_b = fast_exp2(m_b - ms_b);
         m_a = mn_a; m_b = mn_b;
         float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
         for (int nt = 0; nt < KV_TILE / 8; ++nt) {
-            s[nt][0] = exp2f(s[nt][0] - ms_a); s[nt][1] = exp2f(s[nt][1] - ms_a);
-            s[nt][2] = exp2f(s[nt][2] - ms_b); s[nt][3] = exp2f(s[nt][3] - ms_b);
+            s[nt][0] = fast_exp2(s[nt][0] - ms_a); s[nt][1] = fast_exp2(s[nt][1] - ms_a);
+            s[nt][2] = fast_exp2(s[nt][2] - ms_b); s[nt][3] = fast_exp2(s[nt][3] - ms_b);
             sum_a += s[nt][0] + s[nt][1];
             sum_b += s[nt][2] + s[nt][3];
         }
@@ -370,12 +395,12 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
         tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 2));
         const float mn_a = fmaxf(m_a, tmax_a), mn_b = fmaxf(m_b, tmax_b);
         const float ms_a = (mn_a == -INFINITY) ? 0.f : mn_a, ms_b = (mn_b == -INFINITY) ? 0.f : mn_b;
-        const float corr_a = exp2f(m_a - ms_a), corr_b = exp2f(m_b - ms_b);
+        const float corr_a = fast_exp2(m_a - ms_a), corr_b = fast_exp2(m_b - ms_b);
         m_a = mn_a; m_b = mn_b;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-            s[nt][0] = exp2f(s[nt][0] - ms_a); s[nt][1] = exp2f(s[nt][1] - ms_a);
-            s[nt][2] = exp2f(s[nt][2] - ms_b); s[nt][3] = exp2f(s[nt][3] - ms_b);
+            s[nt][0] = fast_exp2(s[nt][0] - ms_a); s[nt][1] = fast_exp2(s[nt][1] - ms_a);
+            s[nt][2] = fast_exp2(s[nt][2] - ms_b); s[nt][3] = fast_exp2(s[nt][3] - ms_b);
         }
         l_a = l_a * corr_a + (s[0][0] + s[0][1] + s[1][0] + s[1][1]);
         l_b = l_b * corr_b + (s[0][2] + s[0][3] + s[1][2] + s[1][3]);
@@ -422,7 +447,7 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
         float acc = 0.f, sum = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float f = exp2f(wm[w * 16 + r] - ms);
+            const float f = fast_exp2(wm[w * 16 + r] - ms);
             acc += f * wo[(w * 16 + r) * D + col];
             sum += f * wl[w * 16 + r];
         }
@@ -516,7 +541,7 @@ extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const 
                     window, scale)) return -1;
     if (n_q_heads > 65535) QIL_REFUSE("attention: too many heads (%d)", n_q_heads);
     if ((uintptr_t)tile_info & 15) QIL_REFUSE("attention: tile_info must be 16-byte aligned");
-    const int smem = (Q_TILE + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
+    const int smem = ((Q_IN_REGS ? 0 : Q_TILE) + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

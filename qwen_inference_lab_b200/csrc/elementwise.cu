@@ -175,7 +175,8 @@ __global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gate_up, bf16* _
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             const float gv = __bfloat162float(g[k]);
-            const float act = round_to<bf16>(gv / (1.0f + expf(-gv)));
+            // fast exp and divide (a few ulp in float32): the value is rounded to bfloat16 next
+            const float act = round_to<bf16>(__fdividef(gv, 1.0f + __expf(-gv)));
             o[k] = __float2bfloat16_rn(act * __bfloat162float(u[k]));
         }
         *reinterpret_cast<uint4*>(out + row * width + col) = o4;

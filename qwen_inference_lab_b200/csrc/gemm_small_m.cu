@@ -158,7 +158,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
             for (int w = 0; w < GSM_WARPS; ++w) { gate += red[w][r][token]; up += red[w][r + 8][token]; }
             gate = round_to<bf16>(gate);
             up = round_to<bf16>(up);
-            const float act = round_to<bf16>(gate / (1.0f + expf(-gate)));
+            const float act = round_to<bf16>(__fdividef(gate, 1.0f + __expf(-gate)));   // as the stand-alone bfloat16 kernel
             reinterpret_cast<bf16*>(out)[(size_t)token * out_width + col] = __float2bfloat16_rn(act * up);
         }
         return;

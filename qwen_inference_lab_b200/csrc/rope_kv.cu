@@ -81,6 +81,140 @@ __global__ void qk_norm_rope_store_kernel(
     }
 }
 
+// bfloat16 fast path (bfloat16 norm weights, head sizes up to 256, rotary_dim a multiple of 4): a block
+// per token, each warp walks heads warp, warp+8, ...  A lane keeps 2-element vectors (elements 2l, 2l+1
+// of every run of 64 in the rotated half and their partners rotary_dim/2 further on), so every access
+// is a coalesced 128-byte row of 4-byte words.  The arithmetic is packed bfloat16: a product of two
+// bfloat16 values rounded once is what elementwise tensor code computes, and two of them cost one
+// instruction instead of the six that emulating the rounding in float32 takes (the kernel was bound by
+// instruction issue, not by memory, before).
+// HD > 0 fixes the head size at compile time and means that the whole head rotates (rotary_dim == HD):
+// the loops then have no dead iterations and no predicates, which matters because the kernel is bound
+// by instruction issue.  HD == 0 takes any head size up to 256 and any rotary_dim.
+#define ROPE_FAST_MAX_D 256
+template <int HD>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_bf16_kernel(
+    const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ kv_cache,
+    const bf16* __restrict__ q_norm_w, const bf16* __restrict__ k_norm_w, float eps,
+    const float* __restrict__ rope_table, int rotary_dim_arg, int table_rows,
+    const int* __restrict__ positions, const int* __restrict__ token_row,
+    const int* __restrict__ block_table, int table_stride,
+    int n_q_heads, int n_kv_heads, int head_dim_arg, int page_size, int num_pages) {
+    typedef __nv_bfloat162 bf2;
+    const int head_dim = HD ? HD : head_dim_arg;
+    const int rotary_dim = HD ? HD : rotary_dim_arg;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int token = blockIdx.x;
+    const int total_heads = n_q_heads + 2 * n_kv_heads;
+    // the token's position and page first: their latency hides behind the first head's loads
+    int pos = positions[token];
+    const int page = (n_kv_heads > 0) ? block_table[(size_t)token_row[token] * table_stride + pos / page_size] : 0;
+    const int slot = page_size > 0 ? pos % page_size : 0;
+    if (pos >= table_rows && table_rows > 0) pos = table_rows - 1;
+    constexpr int RUNS = HD ? (HD / 2 + 63) / 64 : ROPE_FAST_MAX_D / 2 / 64;   // runs of 64 elements in a rotated half
+    constexpr int REST = ROPE_FAST_MAX_D / 64;              // runs of 64 elements outside the rotated part (value heads)
+
+    // Three heads at a time: all their loads are issued before any is used, so a warp has several
+    // hundred bytes in flight instead of one head's worth (the kernel is bound by latency otherwise).
+    constexpr int U = 3;
+    for (int head0 = warp; head0 < total_heads; head0 += 8 * U) {
+        bf2 lo[U][RUNS], hi[U][RUNS], rest[U][REST];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int head = head0 + 8 * u;
+            if (head >= total_heads) continue;
+            const bool rotate = head < n_q_heads + n_kv_heads && rope_table != nullptr && rotary_dim > 0;
+            const int rot = rotate ? rotary_dim : 0, half = rot / 2;
+            const bf2* src = reinterpret_cast<const bf2*>(qkv + ((size_t)token * total_heads + head) * head_dim);
+#pragma unroll
+            for (int i = 0; i < RUNS; ++i) {
+                const int j = 2 * lane + 64 * i;
+                if (j < half) { lo[u][i] = src[j / 2]; hi[u][i] = src[(j + half) / 2]; }
+            }
+#pragma unroll
+            for (int i = 0; i < REST; ++i) {
+                const int j = rot + 2 * lane + 64 * i;
+                if (j < head_dim) rest[u][i] = src[j / 2];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int head = head0 + 8 * u;
+            if (head >= total_heads) continue;
+            const bool is_q = head < n_q_heads;
+            const bool is_k = !is_q && head < n_q_heads + n_kv_heads;
+            const bf16* norm_w = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+            const bool rotate = (is_q || is_k) && rope_table != nullptr && rotary_dim > 0;
+            const int rot = rotate ? rotary_dim : 0, half = rot / 2;
+            if (norm_w != nullptr) {
+                float sq = 0.f;
+#pragma unroll
+                for (int i = 0; i < RUNS; ++i) {
+                    if (2 * lane + 64 * i < half) {
+                        const float2 a = __bfloat1622float2(lo[u][i]), b = __bfloat1622float2(hi[u][i]);
+                        sq += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < REST; ++i) {
+                    if (rot + 2 * lane + 64 * i < head_dim) {
+                        const float2 a = __bfloat1622float2(rest[u][i]);
+                        sq += a.x * a.x + a.y * a.y;
+                    }
+                }
+                sq = warp_sum(sq);
+                const float scale = rsqrtf(sq / (float)head_dim + eps);   // 2 ulp; the result is rounded to bfloat16
+                const bf2* w2 = reinterpret_cast<const bf2*>(norm_w);
+                auto normed = [&](bf2 v, int j) {     // round(x * scale) in float32, then times the weight in bfloat16
+                    const float2 f = __bfloat1622float2(v);
+                    return __hmul2(__floats2bfloat162_rn(f.x * scale, f.y * scale), w2[j / 2]);
+                };
+#pragma unroll
+                for (int i = 0; i < RUNS; ++i) {
+                    const int j = 2 * lane + 64 * i;
+                    if (j < half) { lo[u][i] = normed(lo[u][i], j); hi[u][i] = normed(hi[u][i], j + half); }
+                }
+#pragma unroll
+                for (int i = 0; i < REST; ++i) {
+                    const int j = rot + 2 * lane + 64 * i;
+                    if (j < head_dim) rest[u][i] = normed(rest[u][i], j);
+                }
+            }
+            bf16* dst;
+            if (is_q) {
+                dst = q_out + ((size_t)token * n_q_heads + head) * head_dim;
+            } else {
+                const int kv_head = is_k ? head - n_q_heads : head - n_q_heads - n_kv_heads;
+                if (page < 0 || page >= num_pages) continue;  // host validation failed; never write outside the pool
+                dst = kv_cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * n_kv_heads + kv_head) * page_size + slot) * head_dim;
+            }
+            bf2* out2 = reinterpret_cast<bf2*>(dst);
+            if (rotate) {
+                const float* cs = rope_table + (size_t)pos * rotary_dim;
+#pragma unroll
+                for (int i = 0; i < RUNS; ++i) {
+                    const int j = 2 * lane + 64 * i;
+                    if (j < half) {
+                        // the table holds values already rounded to bfloat16: the conversion is exact
+                        const float2 cf = *reinterpret_cast<const float2*>(cs + j);
+                        const float2 sf = *reinterpret_cast<const float2*>(cs + half + j);
+                        const bf2 c = __floats2bfloat162_rn(cf.x, cf.y), sn = __floats2bfloat162_rn(sf.x, sf.y);
+                        // each product and the sum round separately, as elementwise tensor code does
+                        out2[j / 2] = __hsub2(__hmul2(lo[u][i], c), __hmul2(hi[u][i], sn));
+                        out2[(j + half) / 2] = __hadd2(__hmul2(lo[u][i], sn), __hmul2(hi[u][i], c));
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < REST; ++i) {
+                const int j = rot + 2 * lane + 64 * i;
+                if (j < head_dim) out2[j / 2] = rest[u][i];
+            }
+        }
+    }
+}
+
 extern "C" int qil_qk_norm_rope_store(
     const void* qkv, void* q_out, void* kv_cache, const void* q_norm_w, const void* k_norm_w,
     int norm_w_dtype, float eps, const float* rope_table, int rotary_dim, int table_rows,
@@ -98,8 +232,25 @@ extern "C" int qil_qk_norm_rope_store(
         QIL_REFUSE("qk_norm_rope_store: a cache and a block table are needed to store keys and values");
     if ((q_norm_w == nullptr) != (k_norm_w == nullptr) && n_kv_heads > 0)
         QIL_REFUSE("qk_norm_rope_store: give both norm weights or neither");
-    const int warps = 4;
     const int total_heads = n_q_heads + 2 * n_kv_heads;
+    if (act_dtype == QIL_BF16 && (q_norm_w == nullptr || norm_w_dtype == QIL_BF16) &&
+        head_dim <= ROPE_FAST_MAX_D && head_dim % 2 == 0 && rotary_dim % 4 == 0 &&
+        (rope_table == nullptr || rotary_dim == 0 || ((uintptr_t)rope_table & 7) == 0) &&
+        (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)kv_cache | (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) & 3) == 0) {
+        dim3 fast_grid(n_tokens);
+#define QIL_ROPE_FAST(HD)                                                                                   \
+        qk_norm_rope_store_bf16_kernel<HD><<<fast_grid, 256, 0, stream>>>(                                     \
+            (const bf16*)qkv, (bf16*)q_out, (bf16*)kv_cache, (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, \
+            rope_table, rotary_dim, table_rows, positions, token_row, block_table, table_stride,               \
+            n_q_heads, n_kv_heads, head_dim, page_size, num_pages)
+        const bool whole = rope_table != nullptr && rotary_dim == head_dim;
+        if (whole && head_dim == 128) QIL_ROPE_FAST(128);
+        else if (whole && head_dim == 64) QIL_ROPE_FAST(64);
+        else QIL_ROPE_FAST(0);
+#undef QIL_ROPE_FAST
+        QIL_CHECK_LAUNCH();
+    }
+    const int warps = 4;
     dim3 grid(n_tokens, (total_heads + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
     QIL_DISPATCH_2(act_dtype, norm_w_dtype,
