@@ -299,6 +299,8 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     bf16* sK = sQ + 16 * LDS;                           // [2][64][LDS]
     bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
     int* s_pages = reinterpret_cast<int*>(sV + 2 * KV_TILE * LDS);   // [span_len / page_size + 2]
+    qil_wait_for_producer();
+    qil_release_consumer();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = p.n_q_heads / p.n_kv_heads;
     const int chunks = (group + 15) / 16;
@@ -462,6 +464,8 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
 __global__ void __launch_bounds__(128)
 attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, const float* __restrict__ part_o,
                          const float* __restrict__ part_ml, int n_spans, int span_len) {
+    qil_wait_for_producer();
+    qil_release_consumer();
     const int head = blockIdx.x, d_idx = blockIdx.y;
     const int4 info = decode_info[d_idx];
     const int n = info.x, pos = info.y;
@@ -575,13 +579,13 @@ extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const i
         if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = smem;
     }
-    attn_decode_span_kernel<<<dim3(n_spans, n_kv_heads * chunks, n_decode), 128, smem, stream>>>(
-        p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len);
+    qil_launch_chained(attn_decode_span_kernel, dim3(n_spans, n_kv_heads * chunks, n_decode), dim3(128), smem, stream,
+                       p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len);
     {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }
     }
-    attn_decode_merge_kernel<<<dim3(n_q_heads, n_decode), 128, 0, stream>>>(p, (const int4*)decode_info, part_o,
-                                                                           part_ml, n_spans, span_len);
+    qil_launch_chained(attn_decode_merge_kernel, dim3(n_q_heads, n_decode), dim3(128), 0, stream,
+                       p, (const int4*)decode_info, (const float*)part_o, (const float*)part_ml, n_spans, span_len);
     QIL_CHECK_LAUNCH();
 }

@@ -40,6 +40,40 @@ extern thread_local char qil_error_text[512];
         return 0;                                                        \
     } while (0)
 
+// Programmatic dependent launch.  A kernel launched through qil_launch_chained may begin while the
+// kernel before it on the stream is still finishing: everything it does before qil_wait_for_producer()
+// (fetching weights, which no kernel writes) overlaps that tail; after the wait, all memory the
+// earlier kernels wrote is visible.  qil_release_consumer() lets the kernel after this one start as
+// soon as every block of this one is past it.  Launched the ordinary way both are no-ops.
+__device__ __forceinline__ void qil_wait_for_producer() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void qil_release_consumer() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+#include <stdlib.h>
+static inline bool qil_chaining_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = getenv("QIL_CHAINED_LAUNCH");
+        enabled = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t qil_launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                             cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = qil_chaining_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }

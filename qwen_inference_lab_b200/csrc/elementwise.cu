@@ -25,6 +25,8 @@ __global__ void embed_gather_kernel(const W* __restrict__ table, const int* __re
 // bfloat16 table and output with a width that allows 16-byte copies
 __global__ void embed_gather_bf16x8_kernel(const bf16* __restrict__ table, const int* __restrict__ ids,
                                            bf16* __restrict__ out, int width, int vocab) {
+    qil_wait_for_producer();
+    qil_release_consumer();
     const int row = blockIdx.x;
     int id = ids[row];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -39,7 +41,8 @@ extern "C" int qil_embed_gather(const void* table, int table_dtype, const int* i
     if (width <= 0 || vocab <= 0) QIL_REFUSE("embed_gather: width %d vocab %d", width, vocab);
     if (out_dtype == QIL_BF16 && table_dtype == QIL_BF16 && width % 8 == 0 &&
         (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
-        embed_gather_bf16x8_kernel<<<n_rows, 128, 0, stream>>>((const bf16*)table, ids, (bf16*)out, width, vocab);
+        qil_launch_chained(embed_gather_bf16x8_kernel, dim3(n_rows), dim3(128), 0, stream,
+                           (const bf16*)table, ids, (bf16*)out, width, vocab);
         QIL_CHECK_LAUNCH();
     }
     QIL_DISPATCH_2(out_dtype, table_dtype,
@@ -79,6 +82,8 @@ __global__ void __launch_bounds__(256)
 rmsnorm_bf16x8_kernel(const bf16* __restrict__ x, const W* __restrict__ weight, const int* __restrict__ rows,
                       bf16* __restrict__ out, int width, float eps) {
     __shared__ float scratch[32];
+    qil_wait_for_producer();
+    qil_release_consumer();
     const int r = blockIdx.x;
     const int src_row = rows ? rows[r] : r;
     const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)src_row * width);
@@ -123,9 +128,11 @@ extern "C" int qil_rmsnorm(const void* x, const void* weight, const int* rows, v
     if (act_dtype == QIL_BF16 && width % 8 == 0 && width <= 256 * 8 * RMS_VPT &&
         (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
         if (weight_dtype == QIL_BF16)
-            rmsnorm_bf16x8_kernel<bf16><<<n_rows, 256, 0, stream>>>((const bf16*)x, (const bf16*)weight, rows, (bf16*)out, width, eps);
+            qil_launch_chained(rmsnorm_bf16x8_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream,
+                               (const bf16*)x, (const bf16*)weight, rows, (bf16*)out, width, eps);
         else if (weight_dtype == QIL_F32)
-            rmsnorm_bf16x8_kernel<float><<<n_rows, 256, 0, stream>>>((const bf16*)x, (const float*)weight, rows, (bf16*)out, width, eps);
+            qil_launch_chained(rmsnorm_bf16x8_kernel<float>, dim3(n_rows), dim3(256), 0, stream,
+                               (const bf16*)x, (const float*)weight, rows, (bf16*)out, width, eps);
         else QIL_REFUSE("unknown dtype code %d", weight_dtype);
         QIL_CHECK_LAUNCH();
     }

@@ -44,11 +44,12 @@ __device__ __forceinline__ void gsm_cp_async16(void* smem, const void* gmem, boo
 // Queue one stage: weight rows n0..n0+15 and, when XROWS > 0, the activations of tokens 0..XROWS-1
 // (stage rows 16..), k-values k0..k0+511.  128 threads, 64 pieces of 16 bytes a row: a warp request
 // covers 512 contiguous bytes of one row.
-template <int XROWS>
+// FIRST_ROW..LAST_ROW select weight rows (0..15), activation rows (16..) or both.
+template <int FIRST_ROW, int LAST_ROW>
 __device__ __forceinline__ void gsm_issue_stage(const bf16* __restrict__ W, const bf16* __restrict__ x,
                                                 unsigned char* stage, int n0, int N, int M, int K, int k0, int tid) {
 #pragma unroll
-    for (int i = 0; i < (GSM_ROWS + XROWS) * 64 / 128; ++i) {
+    for (int i = FIRST_ROW * 64 / 128; i < LAST_ROW * 64 / 128; ++i) {
         const int idx = i * 128 + tid;
         const int row = idx >> 6, piece = idx & 63;
         const int k = k0 + piece * 8;
@@ -77,10 +78,21 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
     const int n0 = blockIdx.x * GSM_ROWS;
     const int stages_total = (K + GSM_STAGE_K - 1) / GSM_STAGE_K;
 
-    // weights do not depend on the kernel before this one: get them moving first
+    // Weights do not depend on the kernel before this one: their first stages are requested before the
+    // wait for that kernel, the activations (its output) right after.  Groups: W0..W(S-2), X0..X(S-2),
+    // then one group per later stage; "at most S-2 groups pending" still means "stage s has landed".
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < stages_total) gsm_issue_stage<XROWS>(W, x, ring + s * STAGE_BYTES, n0, N, M, K, s * GSM_STAGE_K, tid);
+        if (s < stages_total)
+            gsm_issue_stage<0, GSM_ROWS>(W, x, ring + s * STAGE_BYTES, n0, N, M, K, s * GSM_STAGE_K, tid);
+        asm volatile("cp.async.commit_group;\n" ::);
+    }
+    qil_wait_for_producer();
+    qil_release_consumer();
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (XS && s < stages_total)
+            gsm_issue_stage<GSM_ROWS, GSM_ROWS + XROWS>(W, x, ring + s * STAGE_BYTES, n0, N, M, K, s * GSM_STAGE_K, tid);
         asm volatile("cp.async.commit_group;\n" ::);
     }
 
@@ -103,7 +115,8 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
         {
             const int next = s + STAGES - 1;
             if (next < stages_total)
-                gsm_issue_stage<XROWS>(W, x, ring + (next % STAGES) * STAGE_BYTES, n0, N, M, K, next * GSM_STAGE_K, tid);
+                gsm_issue_stage<0, GSM_ROWS + XROWS>(W, x, ring + (next % STAGES) * STAGE_BYTES, n0, N, M, K,
+                                                     next * GSM_STAGE_K, tid);
             asm volatile("cp.async.commit_group;\n" ::);
         }
         const unsigned char* stage = ring + (s % STAGES) * STAGE_BYTES;
@@ -200,10 +213,10 @@ extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, 
         configured = true;
     }
     if (M <= 8)
-        gemm_small_m_kernel<1, 1><<<blocks, GSM_WARPS * 32, smem_staged1, stream>>>(
+        qil_launch_chained(gemm_small_m_kernel<1, 1>, dim3(blocks), dim3(GSM_WARPS * 32), smem_staged1, stream,
             (const bf16*)x, (const bf16*)W, (const bf16*)bias, (const bf16*)residual, out, M, N, K, out_f32, silu_pairs);
     else
-        gemm_small_m_kernel<2, 1><<<blocks, GSM_WARPS * 32, smem_staged2, stream>>>(
+        qil_launch_chained(gemm_small_m_kernel<2, 1>, dim3(blocks), dim3(GSM_WARPS * 32), smem_staged2, stream,
             (const bf16*)x, (const bf16*)W, (const bf16*)bias, (const bf16*)residual, out, M, N, K, out_f32, silu_pairs);
     QIL_CHECK_LAUNCH();
 }

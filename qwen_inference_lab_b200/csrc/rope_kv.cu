@@ -104,6 +104,8 @@ qk_norm_rope_store_bf16_kernel(
     typedef __nv_bfloat162 bf2;
     const int head_dim = HD ? HD : head_dim_arg;
     const int rotary_dim = HD ? HD : rotary_dim_arg;
+    qil_wait_for_producer();
+    qil_release_consumer();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int token = blockIdx.x;
     const int total_heads = n_q_heads + 2 * n_kv_heads;
@@ -239,7 +241,7 @@ extern "C" int qil_qk_norm_rope_store(
         (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)kv_cache | (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) & 3) == 0) {
         dim3 fast_grid(n_tokens);
 #define QIL_ROPE_FAST(HD)                                                                                   \
-        qk_norm_rope_store_bf16_kernel<HD><<<fast_grid, 256, 0, stream>>>(                                     \
+        qil_launch_chained(qk_norm_rope_store_bf16_kernel<HD>, fast_grid, dim3(256), 0, stream,                \
             (const bf16*)qkv, (bf16*)q_out, (bf16*)kv_cache, (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, \
             rope_table, rotary_dim, table_rows, positions, token_row, block_table, table_stride,               \
             n_q_heads, n_kv_heads, head_dim, page_size, num_pages)
