@@ -1,0 +1,342 @@
+// C[M,N] = A[M,K] * W[N,K]^T (+ bias) (+ residual) in bfloat16 with float32
+// accumulation on the fifth-generation tensor cores: the projections of prompt
+// portions (M from a few dozen to thousands of tokens).
+//
+// Blackwell-native structure, one persistent block per SM, 192 threads:
+//   warp 0      one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a
+//               128 x 64 tile of A and a 256 x 64 tile of W per stage into a 4-stage ring and
+//               arms the stage's mbarrier with the byte count;
+//   warp 1      one thread issues tcgen05.mma (128 x 256 x 16, operands from shared memory
+//               through matrix descriptors, accumulator in tensor memory) four times per stage,
+//               then tcgen05.commit, which frees the stage when the MMAs have read it; the warp
+//               also allocates and frees the 512 columns of tensor memory;
+//   warps 2-5   read the finished accumulator with tcgen05.ld (each warp its quarter of the 128
+//               lanes), apply the epilogue and store bfloat16; meanwhile warp 1 already fills
+//               the other half of tensor memory with the next tile.
+// Tiles go round-robin over the blocks: tile = blockIdx.x + i * gridDim.x, tokens fastest, so
+// blocks that run together share the same weight columns in L2.
+//
+// Epilogues: bias, residual (may alias out), or `silu_pairs`: W's rows are stored as groups of
+// [8 gate rows, 8 up rows] and the kernel writes silu(gate) * up, N/2 values per token
+// (qil/model.py:71), so the [M, 2I] intermediate never exists in memory.
+//
+// Every wait on an mbarrier is bounded.  A wait that runs out records its place in the error
+// word, the role stops issuing, every role runs out in turn, the producer drains its copies in
+// flight (again bounded), the tensor memory is freed and the kernel returns; the host reads the
+// error word.  No multicast loads are used.
+#include "common.cuh"
+#include <cuda.h>
+
+QIL_ERROR_STORAGE
+
+#define TC_BM 128
+#define TC_BN 256
+#define TC_BK 64
+#define TC_STAGES 4
+#define TC_A_BYTES (TC_BM * TC_BK * 2)
+#define TC_B_BYTES (TC_BN * TC_BK * 2)
+#define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
+#define TC_WAIT_CYCLES 2000000000ll      // about a second
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned done;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait: false when the barrier did not complete in about a second.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > TC_WAIT_CYCLES) return false;
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(smem_u32(smem)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte swizzle, groups of 8
+// rows 1024 bytes apart (the layout a TMA load with CU_TENSOR_MAP_SWIZZLE_128B writes).
+__device__ __forceinline__ unsigned long long umma_desc(unsigned smem_addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);          // start address, 16-byte units
+    d |= (unsigned long long)1 << 16;                                // leading byte offset (unused with swizzle)
+    d |= (unsigned long long)(1024 >> 4) << 32;                      // stride byte offset: 8 rows
+    d |= (unsigned long long)1 << 46;                                // descriptor version of sm_100
+    d |= (unsigned long long)2 << 61;                                // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M = 128, N = 256.
+__device__ __forceinline__ unsigned umma_idesc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TC_BN >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_load_32(unsigned taddr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct TcShared {
+    unsigned long long full[TC_STAGES];
+    unsigned long long empty[TC_STAGES];
+    unsigned long long acc_full[2];
+    unsigned long long acc_empty[2];
+    unsigned tmem_base;
+    unsigned pad;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const bf16* __restrict__ bias, const bf16* residual, bf16* out,
+               int M, int N, int K, int silu_pairs, int* error_word) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    TcShared* sh = reinterpret_cast<TcShared*>(tiles + TC_STAGES * TC_STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + TC_BN - 1) / TC_BN;
+    const int n_tiles = tiles_m * tiles_n;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&sh->acc_full[a], 1); mbar_init(&sh->acc_empty[a], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&sh->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = sh->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_w) : "memory");
+            int stage = 0;
+            unsigned phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TC_BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&sh->empty[stage], phase ^ 1)) { atomicExch(error_word, 1); ok = false; break; }
+                    mbar_arrive_expect_tx(&sh->full[stage], TC_STAGE_BYTES);
+                    unsigned char* a_dst = tiles + stage * TC_STAGE_BYTES;
+                    tma_load_2d(a_dst, &map_a, &sh->full[stage], kb * TC_BK, m0);
+                    tma_load_2d(a_dst + TC_A_BYTES, &map_w, &sh->full[stage], kb * TC_BK, n0);
+                    if (++stage == TC_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            // copies still in flight land in this block's shared memory: wait for them (bounded)
+            // before the block may leave, whether or not anyone consumes them
+            for (int i = 0; i < TC_STAGES; ++i) {
+                if (!mbar_wait(&sh->empty[stage], phase ^ 1)) { atomicExch(error_word, 2); break; }
+                if (++stage == TC_STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const unsigned idesc = umma_idesc();
+            int stage = 0, acc = 0;
+            unsigned phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1)) { atomicExch(error_word, 3); ok = false; break; }
+                tc_fence_after();
+                const unsigned tmem_d = tmem_base + (unsigned)acc * TC_BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&sh->full[stage], phase)) { atomicExch(error_word, 4); ok = false; break; }
+                    tc_fence_after();
+                    const unsigned a_addr = smem_u32(tiles + stage * TC_STAGE_BYTES);
+                    const unsigned b_addr = a_addr + TC_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        // 16 k-values are 32 bytes: advance the start address inside the swizzled row
+                        umma_bf16(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc,
+                                  (kb | k) ? 1u : 0u);
+                    }
+                    umma_commit(&sh->empty[stage]);      // the stage is free once these MMAs have read it
+                    if (++stage == TC_STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(&sh->acc_full[acc]);          // the accumulator is complete once all MMAs are done
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+    } else {
+        const int quarter = warp & 3;                      // the TMEM lanes this warp may read
+        int acc = 0;
+        unsigned acc_phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TC_BN;
+            if (!mbar_wait(&sh->acc_full[acc], acc_phase)) { if (lane == 0) atomicExch(error_word, 5); ok = false; break; }
+            tc_fence_after();
+            const int m = m0 + quarter * 32 + lane;
+            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)acc * TC_BN;
+#pragma unroll 1
+            for (int c = 0; c < TC_BN / 32; ++c) {
+                float v[32];
+                __syncwarp();                              // the load below is a warp-wide instruction
+                tmem_load_32(taddr + c * 32, v);
+                const int n = n0 + c * 32;
+                if (m >= M || n >= N) {
+                    // nothing to store for this lane
+                } else if (silu_pairs) {
+                    // columns come as [8 gate, 8 up] groups: 32 columns give 16 outputs
+                    const int out_width = N / 2;
+                    bf16* dst = out + (size_t)m * out_width + n / 2;
+#pragma unroll
+                    for (int grp = 0; grp < 2; ++grp) {
+                        uint4 packed;
+                        bf16* o = reinterpret_cast<bf16*>(&packed);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float gate = round_to<bf16>(v[grp * 16 + i]);
+                            const float up = round_to<bf16>(v[grp * 16 + 8 + i]);
+                            const float act = round_to<bf16>(__fdividef(gate, 1.0f + __expf(-gate)));
+                            o[i] = __float2bfloat16_rn(act * up);
+                        }
+                        if (n + grp * 16 < N) *reinterpret_cast<uint4*>(dst + grp * 8) = packed;
+                    }
+                } else {
+                    bf16* dst = out + (size_t)m * N + n;
+                    const bf16* res = residual ? residual + (size_t)m * N + n : nullptr;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (n + q * 8 >= N) break;
+                        uint4 packed, rv = make_uint4(0u, 0u, 0u, 0u);
+                        if (res) rv = *reinterpret_cast<const uint4*>(res + q * 8);
+                        const bf16* r8 = reinterpret_cast<const bf16*>(&rv);
+                        bf16* o = reinterpret_cast<bf16*>(&packed);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float x = v[q * 8 + i];
+                            if (bias) x += __bfloat162float(bias[n + q * 8 + i]);
+                            if (res) x = __bfloat162float(r8[i]) + x;
+                            o[i] = __float2bfloat16_rn(x);
+                        }
+                        *reinterpret_cast<uint4*>(dst + q * 8) = packed;
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
+            status == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// A row-major bfloat16 matrix [rows, cols] seen through boxes of [box_rows, 64] with 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
+    EncodeTiledFn encode = encode_tiled();
+    if (encode == nullptr) QIL_REFUSE("gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) QIL_REFUSE("gemm_tc: cuTensorMapEncodeTiled failed with %d for a [%d, %d] matrix", (int)r, rows, cols);
+    return 0;
+}
+
+extern "C" int qil_gemm_tc_min_rows() { return 17; }
+
+// error_word: a device int the caller zeroes once and reads after synchronising; non-zero means a
+// bounded wait inside the kernel ran out (1-2 producer, 3-4 MMA issuer, 5 epilogue).
+extern "C" int qil_gemm_tc(const void* a, const void* w, const void* bias, const void* residual, void* out,
+                           int M, int N, int K, int silu_pairs, int sm_count, int* error_word, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8) QIL_REFUSE("gemm_tc: K %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+    if (N % 8) QIL_REFUSE("gemm_tc: N %d must be a multiple of 8", N);
+    if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out | (uintptr_t)residual) & 15)
+        QIL_REFUSE("gemm_tc: operands must be 16-byte aligned");
+    if (silu_pairs && (N % 16 || bias != nullptr || residual != nullptr))
+        QIL_REFUSE("gemm_tc: silu_pairs needs N %% 16 == 0 and neither bias nor residual");
+    if (error_word == nullptr || sm_count <= 0) QIL_REFUSE("gemm_tc: needs an error word and the SM count");
+    CUtensorMap map_a, map_w;
+    if (make_map(&map_a, a, M, K, TC_BM)) return -1;
+    if (make_map(&map_w, w, N, K, TC_BN)) return -1;
+    const int smem = TC_STAGES * TC_STAGE_BYTES + (int)sizeof(TcShared) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) QIL_REFUSE("gemm_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int n_tiles = ((M + TC_BM - 1) / TC_BM) * ((N + TC_BN - 1) / TC_BN);
+    const int blocks = n_tiles < sm_count ? n_tiles : sm_count;
+    gemm_tc_kernel<<<blocks, 192, smem, stream>>>(map_a, map_w, (const bf16*)bias, (const bf16*)residual, (bf16*)out,
+                                                  M, N, K, silu_pairs, error_word);
+    QIL_CHECK_LAUNCH();
+}

@@ -14,6 +14,7 @@ from __future__ import annotations
 from time import perf_counter
 
 from ..cache import CacheManager
+from ..kernels import gemm_tc
 from ..sampling import Sampler
 from .scheduler import Request, Scheduler
 from .step import StepEntry, StepRunner
@@ -81,6 +82,8 @@ class Engine:
             if ready:
                 tokens = self.sampler.choose(logits, [r.temperature for r in ready], [r.seed for r in ready],
                                              [len(r.output) for r in ready])
+            if sum(len(work.tokens) for work in plan) >= gemm_tc.MIN_ROWS:
+                gemm_tc.check()      # the tensor-core kernel's bounded waits report through an error word
         except Exception as error:
             for work in plan:
                 requests[work.request_id].error = str(error)

@@ -44,6 +44,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     import torch
 
     from ..cache import CacheManager
+    from ..kernels import gemm_tc
     from ..loading import load_model, resolve_dtype
     from .step import StepEntry, StepRunner
 
@@ -71,6 +72,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
             logits = runner.run(entries)
             if logits is not None:
                 data = logits.detach().to(torch.float32).cpu().contiguous().numpy()
+                gemm_tc.check()
                 data.astype("<f4", copy=False).tofile(args.out / f"{step['step']}.f32")
         for request_id in step.get("end", []):
             if request_id in cache.rows:

@@ -1,0 +1,80 @@
+"""The tcgen05/TMA matrix product for prompt portions (bfloat16, float32 accumulation in tensor memory).
+
+``gemm_tc(a, w, ...)`` computes ``a @ w.T`` with the epilogues of :func:`ops.gemm_small_m`.  The
+kernel's mbarrier waits are bounded; if one runs out the kernel records where in an error word and
+returns.  ``check()`` reads that word (it synchronises) and raises if it is set.
+"""
+from __future__ import annotations
+
+from ctypes import c_int, c_void_p
+
+import torch
+
+from . import build
+from .ops import KernelError, _check, _need, _p, _stream
+
+_lib = None
+_error_word = None
+_sm_count = None
+MIN_ROWS = 17
+
+
+def library():
+    global _lib
+    if _lib is None:
+        _lib = build.load("qil_gemm_tc", ["gemm_tc.cu"])
+    return _lib
+
+
+def error_word(device):
+    global _error_word, _sm_count
+    if _error_word is None:
+        _error_word = torch.zeros(1, dtype=torch.int32, device=device)
+        _sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+    return _error_word
+
+
+def usable(a, weight) -> bool:
+    """bfloat16 operands, enough rows to fill a tile's worth of work, 16-byte rows."""
+    return (a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and a.shape[0] >= MIN_ROWS
+            and weight.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0 and a.is_contiguous())
+
+
+def gemm_tc(a, weight, bias=None, residual=None, out=None, silu_pairs=False):
+    """out = a @ weight.T (+ bias) (+ residual); with ``silu_pairs`` (weight rows as [8 gate, 8 up] groups)
+    out = silu(gate) * up of width N/2.  ``residual`` may be ``out``."""
+    _need(a, "a", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
+    m, k = a.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"gemm_tc: a {tuple(a.shape)} against weight {tuple(weight.shape)}")
+    out_shape = (m, n // 2) if silu_pairs else (m, n)
+    if bias is not None:
+        _need(bias, "bias", torch.bfloat16, 1)
+    if residual is not None:
+        _need(residual, "residual", torch.bfloat16, 2)
+        if residual.shape != out_shape:
+            raise KernelError("gemm_tc: residual has the wrong shape")
+    if out is None:
+        out = torch.empty(out_shape, dtype=torch.bfloat16, device=a.device)
+    _need(out, "out", torch.bfloat16, 2)
+    if out.shape != out_shape:
+        raise KernelError("gemm_tc: out has the wrong shape")
+    word = error_word(a.device)
+    lib = library()
+    _check(lib, lib.qil_gemm_tc(_p(a), _p(weight), _p(bias), _p(residual), _p(out), c_int(m), c_int(n), c_int(k),
+                                c_int(1 if silu_pairs else 0), c_int(_sm_count), _p(word), _stream()), "gemm_tc")
+    return out
+
+
+def check() -> None:
+    """Raise if a bounded wait inside any earlier gemm_tc launch ran out (synchronises the device)."""
+    if _error_word is None:
+        return
+    code = int(_error_word.item())
+    if code:
+        _error_word.zero_()
+        where = {1: "producer waiting for a free stage", 2: "producer draining its copies",
+                 3: "MMA issuer waiting for a free accumulator", 4: "MMA issuer waiting for a stage's data",
+                 5: "epilogue waiting for the accumulator"}.get(code, "unknown place")
+        raise KernelError(f"gemm_tc: a wait inside the kernel ran out ({where}, code {code})")

@@ -1,13 +1,15 @@
 """Gated feed-forward: ``down(silu(gate(x)) * up(x))`` (qil/model.py:38-40,70-71).
 
 gate and up are one stacked product; the activation rounds ``silu(gate)`` to the
-activation dtype before the multiply, as elementwise tensor code does.
+activation dtype before the multiply, as elementwise tensor code does.  In
+bfloat16 the product and the activation are one kernel: the weight-streaming
+kernel for a decode step's few rows, the tcgen05 kernel for prompt portions.
 """
 from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import gemm_tc, ops
 from .base import FeedForward
 from .linear import Linear, StackedLinear
 
@@ -41,6 +43,10 @@ class GatedMLP(FeedForward):
     def forward(self, ctx, x, residual=None):
         if self.pairs8 and ops.small_m_ok(x, self.gate_up._w):
             hidden = ops.gemm_small_m(x, self.gate_up._w, silu_pairs=True)
+        elif self.pairs8 and gemm_tc.usable(x, self.gate_up._w):
+            # prompt portions: the tcgen05 kernel applies the activation in its epilogue, so the
+            # [tokens, 2 * intermediate] product never goes to memory
+            hidden = gemm_tc.gemm_tc(x, self.gate_up._w, silu_pairs=True)
         else:
             gate_up = self.gate_up.forward(ctx, x)
             hidden = ops.silu_mul(gate_up, pairs8=self.pairs8)

@@ -362,3 +362,47 @@ def test_gemm_small_m_with_gate_epilogue_and_paired_silu(m, inner, k):
     assert torch.equal(separate.cpu(), expected)
     close(ops().silu_mul(paired_columns.float().contiguous().cuda(), pairs8=True),
           torch.nn.functional.silu(gate.float()) * up.float(), torch.float32, scale=2)
+
+
+@pytest.mark.parametrize("m,n,k", [(17, 8, 8), (128, 256, 64), (100, 264, 200), (300, 520, 1000), (2048, 1024, 4096)])
+def test_gemm_tensor_memory(m, n, k):
+    """The tcgen05/TMA kernel: plain, with bias and residual, in place, at sizes that are no multiple of a tile."""
+    from qwen_inference_lab_b200.kernels import gemm_tc
+    torch.manual_seed(11)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    w = (torch.randn(n, k) * 0.1).to(torch.bfloat16)
+    bias = (torch.randn(n) * 0.1).to(torch.bfloat16)
+    residual = torch.randn(m, n).to(torch.bfloat16)
+    product = a.double() @ w.double().t()
+    scale = float(product.abs().max()) / 2
+    close(gemm_tc.gemm_tc(a.cuda(), w.cuda()), product.float(), torch.bfloat16, scale=scale)
+    close(gemm_tc.gemm_tc(a.cuda(), w.cuda(), bias=bias.cuda(), residual=residual.cuda()),
+          (product + bias.double() + residual.double()).float(), torch.bfloat16, scale=scale)
+    buffer = residual.cuda().clone()
+    gemm_tc.gemm_tc(a.cuda(), w.cuda(), residual=buffer, out=buffer)
+    close(buffer, (product + residual.double()).float(), torch.bfloat16, scale=scale)
+    torch.cuda.synchronize()
+    gemm_tc.check()
+
+
+@pytest.mark.parametrize("m,inner,k", [(17, 8, 16), (130, 200, 96), (512, 1024, 512)])
+def test_gemm_tensor_memory_with_gate_epilogue(m, inner, k):
+    from qwen_inference_lab_b200.kernels import gemm_tc
+    torch.manual_seed(12)
+    a = torch.randn(m, k).to(torch.bfloat16)
+    gate_w = (torch.randn(inner, k) * 0.2).to(torch.bfloat16)
+    up_w = (torch.randn(inner, k) * 0.2).to(torch.bfloat16)
+    gate = (a.float() @ gate_w.float().t()).to(torch.bfloat16)
+    up = (a.float() @ up_w.float().t()).to(torch.bfloat16)
+    expected = torch.nn.functional.silu(gate) * up
+    paired = torch.cat([gate_w, up_w]).view(2, inner // 8, 8, k).transpose(0, 1).reshape(2 * inner, k).contiguous()
+    fused = gemm_tc.gemm_tc(a.cuda(), paired.cuda(), silu_pairs=True)
+    assert fused.shape == (m, inner)
+    # gate, silu(gate) and the product each round to bfloat16: an element may sit two roundings from the
+    # reference's, so the absolute term scales with the largest value
+    close(fused, expected, torch.bfloat16, scale=max(2.0, float(expected.abs().max()) / 2))
+    # the same rows through the decode kernel's epilogue give the same activations
+    if m <= 16:
+        assert torch.equal(ops().gemm_small_m(a.cuda(), paired.cuda(), silu_pairs=True), fused)
+    torch.cuda.synchronize()
+    gemm_tc.check()
