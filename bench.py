@@ -196,7 +196,7 @@ class OursBench:
         torch.cuda.empty_cache()
         return result
 
-    def prefill(self, tokens_n, reps=5, warmup=3):
+    def prefill(self, tokens_n, reps=9, warmup=4):
         torch = self.torch
         from qwen_inference_lab_b200.cache import CacheManager
         from qwen_inference_lab_b200.engine import StepEntry, StepRunner
@@ -208,6 +208,8 @@ class OursBench:
         prompt = torch.randint(0, self.cfg["vocab_size"], (tokens_n,), generator=generator).tolist()
         times = []
         flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        sampler = ClockSampler()
+        sampler.__enter__()
         for i in range(warmup + reps):
             cache.admit("p")
             flush.zero_()   # a buffer larger than L2 between timed iterations
@@ -220,8 +222,11 @@ class OursBench:
             cache.release("p")
             if i >= warmup:
                 times.append(start.elapsed_time(stop))
+        sampler.__exit__()
+        self.last_prefill_clocks = sampler.summary()
         assert torch.isfinite(logits).all()
         ms = statistics.median(times)
+        self.last_prefill_times = sorted(round(t, 3) for t in times)
         del runner, cache, flush
         torch.cuda.empty_cache()
         return ms
@@ -269,7 +274,8 @@ def run_ours(args):
         print(f"decode batch {batch} context {args.context} layers {cfg['num_hidden_layers']}: {part['ms_per_step']:.3f} ms/step")
         return
     if args.only == "prefill":
-        print(f"prefill {PREFILL_TOKENS} tokens layers {cfg['num_hidden_layers']}: {bench.prefill(PREFILL_TOKENS, reps=2, warmup=3):.3f} ms")
+        ms = bench.prefill(PREFILL_TOKENS, reps=args.steps if args.steps != 32 else 2, warmup=3)
+        print(f"prefill {PREFILL_TOKENS} tokens layers {cfg['num_hidden_layers']}: {ms:.3f} ms (all: {bench.last_prefill_times})")
         return
     main = bench.decode(batch, CONTEXT, args.steps, args.warmup, sample_clocks=True)
     points = {}
@@ -299,7 +305,9 @@ def run_ours(args):
         "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": int(main["launches"]),
         "prefill": {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
-                    "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                    "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "ms_min": bench.last_prefill_times[0], "ms_max": bench.last_prefill_times[-1],
+                    "sm_mhz": bench.last_prefill_clocks["sm_mhz"], "reasons": bench.last_prefill_clocks["reasons"]},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,

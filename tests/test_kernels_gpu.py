@@ -265,7 +265,8 @@ def test_span_choice_fills_the_gpu_and_stays_legal():
         span = attention_mma.choose_span(n_decode, 32, 8, ctx)
         assert span % 64 == 0 and 64 <= span <= attention_mma.MAX_DECODE_SPAN
     assert attention_mma.choose_span(1, 32, 8, 8192) < attention_mma.choose_span(64, 32, 8, 8192)
-    assert attention_mma.choose_span(8, 32, 8, 8192) == 512
+    # batch 8 at context 8192: whole waves of the 148 x 3 blocks a B200 holds (6 or 13 spans of 64 blocks)
+    assert attention_mma.choose_span(8, 32, 8, 8192) in (640, 1408)
 
 
 @pytest.mark.parametrize("form", ["portion", "single"])
