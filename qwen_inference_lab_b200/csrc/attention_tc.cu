@@ -1,0 +1,478 @@
+// Causal grouped-query attention of whole 128-token query tiles over the paged cache on the
+// fifth-generation tensor cores (tcgen05.mma, accumulators in tensor memory, operands brought by
+// TMA), for head size 128 and bfloat16.  Same arithmetic as attention_mma.cu (scores = q k^T *
+// head_dim^-1/2 over keys j <= the token's absolute position, float32 softmax, times v;
+// qil/model.py:59-68); this kernel takes the bulk of long prompt portions, the mma.sync kernel what
+// is left over.
+//
+// One block per (tile of 128 query tokens, query head), 192 threads:
+//   warp 0      one thread issues TMA loads: the query tile once, then per 128 keys the pages of K
+//               and of V (one box per page and 64-wide half of the head, 128-byte swizzle);
+//   warp 1      one thread issues tcgen05.mma: S = Q K^T (128 x 128 x 128) into one of two score
+//               buffers in tensor memory, and O += P V once the softmax warps have published P;
+//               it runs one score tile ahead of the softmax;
+//   warps 2-5   one thread per query row: tcgen05.ld of its 128 scores, mask, running maximum, exp2,
+//               row sum, P as bfloat16 into shared memory in the operand layout of the second MMA,
+//               and the rescale of O in tensor memory when the running maximum moved by more than
+//               2^8 (until then P is computed against the older maximum, which is exact algebra and
+//               safe in float32); finally O / l -> global memory.
+// K tiles are K-major operands and V tiles MN-major operands of the same shared-memory image
+// ([key][64 elements = 128 bytes] x two halves of the head).
+//
+// Every mbarrier wait is bounded (about a second), records its place in the error word when it runs
+// out and makes its role stop; the block then frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+QIL_ERROR_STORAGE
+
+#define AT_D 128
+#define AT_M 128                 // query tokens per block
+#define AT_N 128                 // keys per tile
+#define AT_SLAB (128 * 128)      // bytes of a [128 rows][64 elements] slab
+#define AT_TILE (2 * AT_SLAB)    // a [128][128] bfloat16 tile: two slabs
+#define AT_STAGES 2
+#define AT_WAIT_CYCLES 2000000000ll
+
+__device__ __forceinline__ unsigned at_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void at_mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(at_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void at_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(at_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void at_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(at_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool at_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned done;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(done) : "r"(at_smem(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool at_wait(unsigned long long* bar, unsigned parity) {
+    if (at_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!at_try_wait(bar, parity)) {
+        if (clock64() - start > AT_WAIT_CYCLES) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void at_tma_2d(void* smem, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(at_smem(smem)), "l"((unsigned long long)map), "r"(at_smem(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void at_tma_3d(void* smem, const CUtensorMap* map, unsigned long long* bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+                 ::"r"(at_smem(smem)), "l"((unsigned long long)map), "r"(at_smem(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// K-major operand: rows of 128 bytes (64 elements of k), 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ unsigned long long at_desc_kmajor(unsigned addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
+    d |= (unsigned long long)1 << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+// MN-major operand from the same image: 64 elements of n contiguous (one 128-byte row), rows are k;
+// the next 64 n lie one slab further (leading offset), the next 8 k lie 1024 bytes further (stride offset).
+__device__ __forceinline__ unsigned long long at_desc_mnmajor(unsigned addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
+    d |= (unsigned long long)(AT_SLAB >> 4) << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void at_mma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc, unsigned acc) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void at_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(at_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void at_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void at_tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void at_tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+                 ::"r"(taddr),
+                   "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void at_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void at_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ float at_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct AtShared {
+    unsigned long long q_full;
+    unsigned long long k_full[AT_STAGES], k_empty[AT_STAGES];
+    unsigned long long v_full[AT_STAGES], v_empty[AT_STAGES];
+    unsigned long long s_full[2], s_empty[2];
+    unsigned long long p_full, pv_done;
+    unsigned tmem_base;
+    unsigned pad;
+};
+
+struct AtParams {
+    bf16* out;                  // [N, Hq, 128]
+    const int* block_table;
+    int table_stride;
+    int n_q_heads, n_kv_heads, page_size;
+    float scale_log2;
+    int* error_word;
+};
+
+__global__ void __launch_bounds__(192, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+               AtParams p, const int4* __restrict__ tile_info) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = base;                               // [2 slabs]
+    unsigned char* sK = sQ + AT_TILE;                       // [stages][2 slabs]
+    unsigned char* sV = sK + AT_STAGES * AT_TILE;           // [stages][2 slabs]
+    unsigned char* sP = sV + AT_STAGES * AT_TILE;           // [2 slabs]: keys 0..63, 64..127
+    AtShared* sh = reinterpret_cast<AtShared*>(sP + AT_TILE);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y;
+    const int kv_head = head / (p.n_q_heads / p.n_kv_heads);
+    // tile_info: (first token in the flat batch, its absolute position, 128, block-table row)
+    const int4 info = tile_info[blockIdx.x];
+    const int n0 = info.x, pos0 = info.y;
+    const int hi = pos0 + AT_M - 1;                          // last key any row of the tile may see
+    const int n_tiles = hi / AT_N + 1;
+    const int* table = p.block_table + (size_t)info.w * p.table_stride;
+
+    if (threadIdx.x == 0) {
+        at_mbar_init(&sh->q_full, 1);
+        for (int s = 0; s < AT_STAGES; ++s) {
+            at_mbar_init(&sh->k_full[s], 1); at_mbar_init(&sh->k_empty[s], 1);
+            at_mbar_init(&sh->v_full[s], 1); at_mbar_init(&sh->v_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) { at_mbar_init(&sh->s_full[b], 1); at_mbar_init(&sh->s_empty[b], 4); }
+        at_mbar_init(&sh->p_full, 4);
+        at_mbar_init(&sh->pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(at_smem(&sh->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    at_fence_before();
+    __syncthreads();
+    at_fence_after();
+    const unsigned tmem = sh->tmem_base;
+    const unsigned tmem_s[2] = {tmem, tmem + 128u};
+    const unsigned tmem_o = tmem + 256u;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_q) : "memory");
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_kv) : "memory");
+            // queries: box (64 elements, 1 head, 128 tokens) per half of the head
+            at_expect_tx(&sh->q_full, AT_TILE);
+            at_tma_3d(sQ, &map_q, &sh->q_full, 0, head, n0);
+            at_tma_3d(sQ + AT_SLAB, &map_q, &sh->q_full, 64, head, n0);
+            const int pages_per_tile = AT_N / p.page_size;
+            const int page_bytes = p.page_size * 128;       // one page of one half: page_size rows of 128 bytes
+            bool ok = true;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int stage = j % AT_STAGES;
+                const unsigned parity = ((j / AT_STAGES) & 1) ^ 1;
+                // pages of this tile that exist (positions up to hi); the others are never read unmasked
+                const int first_key = j * AT_N;
+                int pages = pages_per_tile;
+                if (first_key + AT_N - 1 > hi) pages = (hi - first_key) / p.page_size + 1;
+                for (int kv = 0; kv < 2 && ok; ++kv) {
+                    unsigned long long* full = kv == 0 ? &sh->k_full[stage] : &sh->v_full[stage];
+                    unsigned long long* empty = kv == 0 ? &sh->k_empty[stage] : &sh->v_empty[stage];
+                    unsigned char* dst = (kv == 0 ? sK : sV) + stage * AT_TILE;
+                    if (!at_wait(empty, parity)) { atomicExch(p.error_word, 11); ok = false; break; }
+                    at_expect_tx(full, (unsigned)(pages * 2 * page_bytes));
+                    for (int pg = 0; pg < pages; ++pg) {
+                        const int page = table[first_key / p.page_size + pg];
+                        // cache rows of one layer: ((page * 2 + kv) * kv_heads + kv_head) * page_size + slot
+                        const int row = ((page * 2 + kv) * p.n_kv_heads + kv_head) * p.page_size;
+                        at_tma_2d(dst + pg * page_bytes, &map_kv, full, 0, row);
+                        at_tma_2d(dst + AT_SLAB + pg * page_bytes, &map_kv, full, 64, row);
+                    }
+                }
+            }
+            // leave only after the copies have been consumed or have had a second to land
+            for (int j = n_tiles; j < n_tiles + AT_STAGES && ok; ++j) {
+                const int stage = j % AT_STAGES;
+                const unsigned parity = ((j / AT_STAGES) & 1) ^ 1;
+                if (!at_wait(&sh->k_empty[stage], parity) || !at_wait(&sh->v_empty[stage], parity)) {
+                    atomicExch(p.error_word, 12);
+                    break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // both MMAs: M = 128, N = 128, bfloat16 -> float32; the second one reads B (V) MN-major
+            const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_N >> 3) << 17) | ((unsigned)(AT_M >> 4) << 24);
+            const unsigned idesc_pv = idesc_s | (1u << 16);
+            bool ok = at_wait(&sh->q_full, 0);
+            if (!ok) atomicExch(p.error_word, 13);
+            auto issue_scores = [&](int j) -> bool {
+                const int stage = j % AT_STAGES, buf = j & 1;
+                if (!at_wait(&sh->k_full[stage], (j / AT_STAGES) & 1)) { atomicExch(p.error_word, 14); return false; }
+                if (!at_wait(&sh->s_empty[buf], ((j >> 1) & 1) ^ 1)) { atomicExch(p.error_word, 15); return false; }
+                at_fence_after();
+                const unsigned q_addr = at_smem(sQ), k_addr = at_smem(sK + stage * AT_TILE);
+#pragma unroll
+                for (int kk = 0; kk < AT_D / 16; ++kk) {
+                    const unsigned off = (kk >> 2) * AT_SLAB + (kk & 3) * 32;      // half of the head, then 16 elements = 32 bytes
+                    at_mma(tmem_s[buf], at_desc_kmajor(q_addr + off), at_desc_kmajor(k_addr + off), idesc_s, kk ? 1u : 0u);
+                }
+                at_commit(&sh->s_full[buf]);
+                at_commit(&sh->k_empty[stage]);
+                return true;
+            };
+            if (ok) ok = issue_scores(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) { ok = issue_scores(j + 1); if (!ok) break; }
+                const int stage = j % AT_STAGES;
+                if (!at_wait(&sh->v_full[stage], (j / AT_STAGES) & 1)) { atomicExch(p.error_word, 16); ok = false; break; }
+                if (!at_wait(&sh->p_full, j & 1)) { atomicExch(p.error_word, 17); ok = false; break; }
+                at_fence_after();
+                const unsigned p_addr = at_smem(sP), v_addr = at_smem(sV + stage * AT_TILE);
+#pragma unroll
+                for (int kk = 0; kk < AT_N / 16; ++kk) {
+                    // P: 16 keys = 32 bytes inside the key half; V: 16 keys = 16 rows of 128 bytes
+                    const unsigned p_off = (kk >> 2) * AT_SLAB + (kk & 3) * 32;
+                    at_mma(tmem_o, at_desc_kmajor(p_addr + p_off), at_desc_mnmajor(v_addr + kk * 2048), idesc_pv,
+                           (j | kk) ? 1u : 0u);
+                }
+                at_commit(&sh->pv_done);
+                at_commit(&sh->v_empty[stage]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                 // query row of this thread = its TMEM lane
+        const int pos = pos0 + row;
+        const unsigned lane_base = (unsigned)(quarter * 32) << 16;
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int buf = j & 1, stage = j % AT_STAGES;
+            if (!at_wait(&sh->s_full[buf], (j >> 1) & 1)) { if (lane == 0) atomicExch(p.error_word, 21); ok = false; break; }
+            at_fence_after();
+            float s[AT_N];
+#pragma unroll
+            for (int c = 0; c < AT_N / 32; ++c) {
+                unsigned r[32];
+                at_tmem_ld32(tmem_s[buf] + lane_base + c * 32, r);
+                at_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
+            }
+            at_fence_before();
+            __syncwarp();
+            if (lane == 0) at_arrive(&sh->s_empty[buf]);      // the score buffer may be overwritten
+            // scale, mask by absolute position (only tiles that reach past the first row's position need it)
+            const int key0 = j * AT_N;
+            float tmax = -INFINITY;
+            if (key0 + AT_N - 1 <= pos0) {
+#pragma unroll
+                for (int i = 0; i < AT_N; ++i) { s[i] *= p.scale_log2; tmax = fmaxf(tmax, s[i]); }
+            } else {
+#pragma unroll
+                for (int i = 0; i < AT_N; ++i) {
+                    s[i] = (key0 + i <= pos) ? s[i] * p.scale_log2 : -INFINITY;
+                    tmax = fmaxf(tmax, s[i]);
+                }
+            }
+            // O is stable and P's buffer free once the previous tile's second MMA is done
+            if (j > 0 && !at_wait(&sh->pv_done, (j - 1) & 1)) { if (lane == 0) atomicExch(p.error_word, 22); ok = false; break; }
+            at_fence_after();
+            // Move the maximum only when it grew by more than 2^8: until then exp2(s - m_used) <= 256,
+            // harmless in float32 and bfloat16, and O needs no rescale (which costs a TMEM round trip).
+            const bool grow = tmax > m_used + 8.0f;            // also true at the first tile (m_used = -inf)
+            if (__any_sync(0xffffffffu, grow && j > 0)) {
+                const float factor = grow ? at_exp2(m_used - tmax) : 1.0f;     // exp2(-inf) = 0 cannot occur for j > 0 rows with keys
+#pragma unroll 1
+                for (int c = 0; c < AT_D / 32; ++c) {
+                    unsigned r[32];
+                    at_tmem_ld32(tmem_o + lane_base + c * 32, r);
+                    at_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+                    at_tmem_st32(tmem_o + lane_base + c * 32, r);
+                }
+                at_wait_st();
+                if (grow) l *= factor;
+            } else if (grow && j == 0) {
+                // nothing accumulated yet
+            }
+            if (grow) m_used = tmax;
+            const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+            // on the last tile, value rows past the last visible key may hold anything (unwritten slots):
+            // zero them so that 0 * garbage cannot become NaN; they are this thread's key row
+            if (j == n_tiles - 1) {
+                if (!at_wait(&sh->v_full[stage], (j / AT_STAGES) & 1)) { if (lane == 0) atomicExch(p.error_word, 23); ok = false; break; }
+                if (key0 + row > hi) {
+                    unsigned char* v_row = sV + stage * AT_TILE + row * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        *reinterpret_cast<uint4*>(v_row + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        *reinterpret_cast<uint4*>(v_row + AT_SLAB + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            }
+            // P = exp2(s - m) as bfloat16 into the K-major operand image: row `row`, 16-byte chunk c of each
+            // 128-byte half-row goes to chunk (c ^ (row & 7))
+            float sum = 0.f;
+            unsigned char* p_row = sP + row * 128;
+#pragma unroll
+            for (int c = 0; c < AT_N / 8; ++c) {
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { e[i] = at_exp2(s[c * 8 + i] - m_safe); sum += e[i]; }
+                uint4 packed;
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(e[0], e[1]), b1 = __floats2bfloat162_rn(e[2], e[3]);
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(e[4], e[5]), b3 = __floats2bfloat162_rn(e[6], e[7]);
+                packed.x = *reinterpret_cast<unsigned*>(&b0); packed.y = *reinterpret_cast<unsigned*>(&b1);
+                packed.z = *reinterpret_cast<unsigned*>(&b2); packed.w = *reinterpret_cast<unsigned*>(&b3);
+                const int half = c >> 3, chunk = c & 7;
+                *reinterpret_cast<uint4*>(p_row + half * AT_SLAB + ((chunk ^ (row & 7)) << 4)) = packed;
+            }
+            l += sum;
+            // make the shared-memory writes visible to the tensor core's reads, and order the TMEM stores
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            at_fence_before();
+            __syncwarp();
+            if (lane == 0) at_arrive(&sh->p_full);
+        }
+        if (ok) {
+            if (!at_wait(&sh->pv_done, (n_tiles - 1) & 1)) { if (lane == 0) atomicExch(p.error_word, 24); ok = false; }
+        }
+        if (ok) {
+            at_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = p.out + ((size_t)(n0 + row) * p.n_q_heads + head) * AT_D;
+#pragma unroll 1
+            for (int c = 0; c < AT_D / 32; ++c) {
+                unsigned r[32];
+                __syncwarp();
+                at_tmem_ld32(tmem_o + lane_base + c * 32, r);
+                at_wait_ld();
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 packed;
+                    bf16* o = reinterpret_cast<bf16*>(&packed);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(__uint_as_float(r[q * 8 + i]) * inv);
+                    *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = packed;
+                }
+            }
+        }
+    }
+    at_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        at_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*AtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static AtEncodeFn at_encode() {
+    static AtEncodeFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
+            status == cudaDriverEntryPointSuccess)
+            fn = (AtEncodeFn)ptr;
+    }
+    return fn;
+}
+
+extern "C" int qil_attn_tc_head_dim() { return AT_D; }
+
+// q [N, Hq, 128], kv one layer's pages [pages, 2, Hkv, page_size, 128], out [N, Hq, 128], all bfloat16.
+// tile_info int32 [n_tiles, 4] = (first token, its absolute position, 128, block-table row): whole tiles only.
+// page_size must divide 128 and be a multiple of 8.  error_word: a device int, zeroed by the caller once.
+extern "C" int qil_attn_tc_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                   int n_tokens, const int* block_table, int table_stride, int n_q_heads,
+                                   int n_kv_heads, int page_size, int num_pages, float scale, int* error_word,
+                                   cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (n_kv_heads <= 0 || n_q_heads % n_kv_heads) QIL_REFUSE("attn_tc: %d query heads, %d kv heads", n_q_heads, n_kv_heads);
+    if (page_size < 8 || page_size > 128 || 128 % page_size || page_size % 8)
+        QIL_REFUSE("attn_tc: pages of %d positions; this kernel takes 8, 16, 32, 64 or 128", page_size);
+    if (n_q_heads > 65535) QIL_REFUSE("attn_tc: too many heads");
+    if (((uintptr_t)q | (uintptr_t)kv | (uintptr_t)out | (uintptr_t)tile_info) & 15) QIL_REFUSE("attn_tc: operands must be 16-byte aligned");
+    if (error_word == nullptr) QIL_REFUSE("attn_tc: needs an error word");
+    AtEncodeFn encode = at_encode();
+    if (encode == nullptr) QIL_REFUSE("attn_tc: the driver does not offer cuTensorMapEncodeTiled");
+    CUtensorMap map_q, map_kv;
+    {
+        const cuuint64_t dims[3] = {AT_D, (cuuint64_t)n_q_heads, (cuuint64_t)n_tokens};
+        const cuuint64_t strides[2] = {AT_D * 2, (cuuint64_t)n_q_heads * AT_D * 2};
+        const cuuint32_t box[3] = {64, 1, AT_M};
+        const cuuint32_t elem[3] = {1, 1, 1};
+        const CUresult r = encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) QIL_REFUSE("attn_tc: cuTensorMapEncodeTiled failed for the queries (%d)", (int)r);
+    }
+    {
+        const cuuint64_t rows = (cuuint64_t)num_pages * 2 * n_kv_heads * page_size;
+        const cuuint64_t dims[2] = {AT_D, rows};
+        const cuuint64_t strides[1] = {AT_D * 2};
+        const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+        const cuuint32_t elem[2] = {1, 1};
+        const CUresult r = encode(&map_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(kv), dims, strides, box, elem,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) QIL_REFUSE("attn_tc: cuTensorMapEncodeTiled failed for the cache (%d)", (int)r);
+    }
+    AtParams p;
+    p.out = (bf16*)out; p.block_table = block_table; p.table_stride = table_stride;
+    p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.error_word = error_word;
+    const int smem = AT_TILE * (2 + 2 * AT_STAGES) + (int)sizeof(AtShared) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) QIL_REFUSE("attn_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    attn_tc_kernel<<<dim3(n_tiles, n_q_heads), 192, smem, stream>>>(map_q, map_kv, p, (const int4*)tile_info);
+    QIL_CHECK_LAUNCH();
+}

@@ -14,7 +14,7 @@ from __future__ import annotations
 from time import perf_counter
 
 from ..cache import CacheManager
-from ..kernels import gemm_tc
+from ..kernels import attention_tc, gemm_tc
 from ..sampling import Sampler
 from .scheduler import Request, Scheduler
 from .step import StepEntry, StepRunner
@@ -83,7 +83,8 @@ class Engine:
                 tokens = self.sampler.choose(logits, [r.temperature for r in ready], [r.seed for r in ready],
                                              [len(r.output) for r in ready])
             if sum(len(work.tokens) for work in plan) >= gemm_tc.MIN_ROWS:
-                gemm_tc.check()      # the tensor-core kernel's bounded waits report through an error word
+                gemm_tc.check()      # the tensor-memory kernels' bounded waits report through error words
+                attention_tc.check()
         except Exception as error:
             for work in plan:
                 requests[work.request_id].error = str(error)

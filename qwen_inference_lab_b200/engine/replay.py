@@ -44,7 +44,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     import torch
 
     from ..cache import CacheManager
-    from ..kernels import gemm_tc
+    from ..kernels import attention_tc, gemm_tc
     from ..loading import load_model, resolve_dtype
     from .step import StepEntry, StepRunner
 
@@ -73,6 +73,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
             if logits is not None:
                 data = logits.detach().to(torch.float32).cpu().contiguous().numpy()
                 gemm_tc.check()
+                attention_tc.check()
                 data.astype("<f4", copy=False).tofile(args.out / f"{step['step']}.f32")
         for request_id in step.get("end", []):
             if request_id in cache.rows:

@@ -24,6 +24,7 @@ from ..parts.base import StepContext
 from ..utils.staging import PinnedRing
 
 QUERY_TILE = 64          # tokens per query tile of the prompt-portion attention kernel
+BIG_QUERY_TILE = 128     # tokens per query tile of the tensor-memory attention kernel
 
 
 class StepError(ValueError):
@@ -53,7 +54,7 @@ class StepRunner:
         self._ring = PinnedRing() if self.device.type == "cuda" else None
         self._graphs: dict = {}
         self._graph_pool = None
-        self._reserve(8 * max_step_tokens + 8 * cache.max_requests + 64)
+        self._reserve(8 * max_step_tokens + 16 * cache.max_requests + 64)
         self.steps_run = 0
         self.kernel_launches = 0          # this engine's own kernels (library products are not counted)
         self.launches_per_graph: dict = {}
@@ -108,13 +109,26 @@ class StepRunner:
         # the longest tiles of the longest contexts first: they take longest, the short ones fill the gaps
         tiles.sort(key=lambda t: -(t[1] + t[2]))
         tile_info = np.array(tiles, dtype=np.int64).reshape(-1)
+        # the same tokens cut for kernels that take whole tiles of 128 tokens: those tiles, and 64-token
+        # tiles for what they leave over (short segments and the tails of long ones)
+        big, rest = [], []
+        for i in np.nonzero(lens > 1)[0]:
+            whole = int(lens[i]) // BIG_QUERY_TILE * BIG_QUERY_TILE
+            big += [(seg_start[i] + off, starts[i] + off, BIG_QUERY_TILE, rows[i]) for off in range(0, whole, BIG_QUERY_TILE)]
+            rest += [(seg_start[i] + off, starts[i] + off, min(QUERY_TILE, int(lens[i]) - off), rows[i])
+                     for off in range(whole, int(lens[i]), QUERY_TILE)]
+        big.sort(key=lambda t: -(t[1] + t[2]))
+        rest.sort(key=lambda t: -(t[1] + t[2]))
+        big_tile_info = np.array(big, dtype=np.int64).reshape(-1)
+        rest_tile_info = np.array(rest, dtype=np.int64).reshape(-1)
         # single-token segments: (token, its position, block-table row, 0)
         single = np.nonzero(lens == 1)[0]
         decode_info = np.stack([seg_start[single], starts[single], rows[single], np.zeros_like(single)],
                                axis=1).reshape(-1) if len(single) else np.zeros(0, dtype=np.int64)
         sections = [("token_ids", token_ids), ("positions", positions), ("token_row", token_row),
                     ("seg_row", rows), ("seg_start", seg_start), ("seg_len", lens), ("seg_pos0", starts),
-                    ("logit_rows", logit_rows), ("tile_info", tile_info), ("decode_info", decode_info)]
+                    ("logit_rows", logit_rows), ("tile_info", tile_info), ("decode_info", decode_info),
+                    ("big_tile_info", big_tile_info), ("rest_tile_info", rest_tile_info)]
         offsets, total = {}, 0
         for name, values in sections:
             offsets[name] = (total, len(values))
@@ -136,6 +150,8 @@ class StepRunner:
             seg_row=section("seg_row"), seg_start=section("seg_start"), seg_len=section("seg_len"),
             seg_pos0=section("seg_pos0"), n_tiles=offsets["tile_info"][1] // 4, tile_info=section("tile_info"),
             n_decode=offsets["decode_info"][1] // 4, decode_info=section("decode_info"),
+            n_big_tiles=offsets["big_tile_info"][1] // 4, big_tile_info=section("big_tile_info"),
+            n_rest_tiles=offsets["rest_tile_info"][1] // 4, rest_tile_info=section("rest_tile_info"),
             max_context=max_context, h_seg_row=host["seg_row"], h_seg_start=host["seg_start"],
             h_seg_len=host["seg_len"], h_seg_pos0=host["seg_pos0"])
 

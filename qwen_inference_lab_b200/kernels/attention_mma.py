@@ -11,7 +11,7 @@ from ctypes import c_float, c_int, c_void_p
 
 import torch
 
-from . import build
+from . import attention_tc, build
 from .ops import KernelError, _check, _p, _stream
 
 _libs: dict = {}
@@ -103,7 +103,14 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
         raise KernelError("the tensor-core attention takes bfloat16 queries and pages")
     if tuple(cache.pages.shape[1:]) != (2, n_kv_heads, cache.page_size, head_dim):
         raise KernelError(f"attention: cache layout {tuple(cache.pages.shape)}")
-    if ctx.n_tiles:
+    if ctx.n_big_tiles and attention_tc.supports(head_dim, cache.page_size, window):
+        # whole 128-token tiles on tcgen05 with the accumulators in tensor memory, the leftovers below
+        attention_tc.prefill(q, cache.pages, out, ctx.big_tile_info, ctx.n_big_tiles, cache.block_table,
+                             n_q_heads, n_kv_heads, cache.page_size, scale)
+        if ctx.n_rest_tiles:
+            prefill(q, cache.pages, out, ctx.rest_tile_info, ctx.n_rest_tiles, cache.block_table, n_q_heads,
+                    n_kv_heads, head_dim, cache.page_size, window, scale)
+    elif ctx.n_tiles:
         prefill(q, cache.pages, out, ctx.tile_info, ctx.n_tiles, cache.block_table, n_q_heads, n_kv_heads,
                 head_dim, cache.page_size, window, scale)
     if ctx.n_decode:

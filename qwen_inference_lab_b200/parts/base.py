@@ -148,6 +148,11 @@ class StepContext:
     n_decode: int
     decode_info: torch.Tensor        # [n_decode * 4]
     max_context: int                 # largest start+len over the batch's segments (host upper bound)
+    # the multi-token segments cut a second way: whole tiles of 128 tokens, and 64-token tiles for the rest
+    n_big_tiles: int = 0
+    big_tile_info: torch.Tensor = None    # [n_big_tiles * 4], same four ints as tile_info
+    n_rest_tiles: int = 0
+    rest_tile_info: torch.Tensor = None   # [n_rest_tiles * 4]
     h_seg_row: object = None
     h_seg_start: object = None
     h_seg_len: object = None

@@ -407,3 +407,56 @@ def test_gemm_tensor_memory_with_gate_epilogue(m, inner, k):
         assert torch.equal(ops().gemm_small_m(a.cuda(), paired.cuda(), silu_pairs=True), fused)
     torch.cuda.synchronize()
     gemm_tc.check()
+
+
+TENSOR_MEMORY_ATTENTION_CASES = [
+    # n_q, n_kv, lengths, chunk starts (chunk lengths are multiples of 128), page
+    (1, 1, [128], [0], 16),
+    (4, 2, [384, 200], [128, 72], 16),
+    (8, 2, [1024, 133], [0, 5], 8),
+    (4, 4, [700], [60], 64),
+    (6, 1, [2100, 300], [1972, 44], 128),
+    (32, 8, [2048], [0], 16),
+]
+
+
+@pytest.mark.parametrize("case", TENSOR_MEMORY_ATTENTION_CASES,
+                         ids=[f"case{i}" for i in range(len(TENSOR_MEMORY_ATTENTION_CASES))])
+def test_attention_tensor_memory(case):
+    """The tcgen05 kernel on whole 128-token tiles over poisoned, shuffled pages, at positions that are no
+    multiple of anything, against the plain float32 attention."""
+    from qwen_inference_lab_b200.kernels import attention_tc
+    n_q, n_kv, lengths, starts, page = case
+    d = 128
+    q, pool, table, meta, expected = attention_case(n_q, n_kv, d, lengths, starts, torch.bfloat16, page, seed=13)
+    info = []
+    for start, length, pos0, row in zip(meta["seg_start"], meta["seg_len"], meta["seg_pos0"], meta["seg_row"]):
+        assert length % 128 == 0
+        for off in range(0, length, 128):
+            info += [start + off, pos0 + off, 128, row]
+    out = torch.full(q.shape, float("nan"), dtype=torch.bfloat16).cuda()
+    attention_tc.prefill(q.cuda(), pool.cuda(), out, torch.tensor(info, dtype=torch.int32).cuda(), len(info) // 4,
+                         table.cuda(), n_q, n_kv, page, d ** -0.5)
+    torch.cuda.synchronize()
+    attention_tc.check()
+    close(out, expected, torch.bfloat16, scale=2)
+
+
+def test_attention_tensor_memory_far_key_and_big_scores():
+    """One key far back dominates (its value is large), and scores are large enough that the running maximum
+    must move by more than 2^8 between tiles: the lazy rescale of the accumulator has to happen and be right."""
+    from qwen_inference_lab_b200.kernels import attention_tc
+    n_q, n_kv, d, page = 4, 2, 128, 16
+    q, pool, table, meta, expected = attention_case(n_q, n_kv, d, [1300, 256], [1044, 0], torch.bfloat16, page, seed=14,
+                                                    spike=(0, 700))
+    assert expected[:256].abs().mean() > 10
+    info = []
+    for start, length, pos0, row in zip(meta["seg_start"], meta["seg_len"], meta["seg_pos0"], meta["seg_row"]):
+        for off in range(0, length, 128):
+            info += [start + off, pos0 + off, 128, row]
+    out = torch.full(q.shape, float("nan"), dtype=torch.bfloat16).cuda()
+    attention_tc.prefill(q.cuda(), pool.cuda(), out, torch.tensor(info, dtype=torch.int32).cuda(), len(info) // 4,
+                         table.cuda(), n_q, n_kv, page, d ** -0.5)
+    torch.cuda.synchronize()
+    attention_tc.check()
+    close(out, expected, torch.bfloat16, scale=25)
