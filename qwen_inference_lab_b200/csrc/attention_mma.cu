@@ -127,10 +127,11 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
     bf16* sQ = Q_IN_REGS ? sK + KV_TILE * LDS : sV + 2 * KV_TILE * LDS;   // [64][LDS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int head = blockIdx.y;
+    // heads vary fastest, so all heads of the longest tile start first (tiles come sorted, longest first)
+    const int head = blockIdx.x;
     const int kv_head = head / (p.n_q_heads / p.n_kv_heads);
     // tile_info: (first token in the flat batch, its absolute position, rows in the tile, block-table row)
-    const int4 info = tile_info[blockIdx.x];
+    const int4 info = tile_info[blockIdx.y];
     const int n0 = info.x, pos0 = info.y, rows = min(Q_TILE, info.z);
     const int hi = pos0 + rows - 1;
     const int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
@@ -543,7 +544,7 @@ extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const 
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
-    if (n_q_heads > 65535) QIL_REFUSE("attention: too many heads (%d)", n_q_heads);
+    if (n_tiles > 65535) QIL_REFUSE("attention: %d query tiles in one launch; at most 65535", n_tiles);
     if ((uintptr_t)tile_info & 15) QIL_REFUSE("attention: tile_info must be 16-byte aligned");
     const int smem = ((Q_IN_REGS ? 0 : Q_TILE) + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
     static bool configured = false;
@@ -552,7 +553,7 @@ extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const 
         if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    attn_prefill_kernel<<<dim3(n_tiles, n_q_heads), 128, smem, stream>>>(p, (const int4*)tile_info);
+    attn_prefill_kernel<<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info);
     QIL_CHECK_LAUNCH();
 }
 

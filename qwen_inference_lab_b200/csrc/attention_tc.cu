@@ -28,9 +28,15 @@ QIL_ERROR_STORAGE
 
 #define AT_D 128
 #define AT_M 128                 // query tokens per block
-#define AT_N 128                 // keys per tile
-#define AT_SLAB (128 * 128)      // bytes of a [128 rows][64 elements] slab
-#define AT_TILE (2 * AT_SLAB)    // a [128][128] bfloat16 tile: two slabs
+#ifndef AT_N
+#define AT_N 64                  // keys per tile (64: two blocks fit an SM and overlap each other's softmax and MMAs)
+#endif
+#define AT_QSLAB (AT_M * 128)    // bytes of a [128 query rows][64 elements] slab (also of a P slab: 64 keys)
+#define AT_QTILE (2 * AT_QSLAB)  // the query tile: two halves of the head
+#define AT_SLAB (AT_N * 128)     // bytes of a [keys][64 elements] slab of K or V
+#define AT_TILE (2 * AT_SLAB)    // a K or V tile: two halves of the head
+#define AT_PTILE ((AT_N / 64) * AT_QSLAB)   // P: [128 rows][keys], one slab per 64 keys
+#define AT_TMEM_COLS (AT_N == 64 ? 256 : 512)
 #define AT_STAGES 2
 #define AT_WAIT_CYCLES 2000000000ll
 
@@ -130,6 +136,14 @@ __device__ __forceinline__ float at_exp2(float x) {
     return y;
 }
 
+// Optional time stamps of one block's roles (compile with -DAT_TRACE=1): trace[role * 1024 + event].
+#ifdef AT_TRACE
+#define AT_STAMP(role, idx) do { if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (idx) < 1024) \
+    p.trace[(role) * 1024 + (idx)] = clock64(); } while (0)
+#else
+#define AT_STAMP(role, idx) do { } while (0)
+#endif
+
 struct AtShared {
     unsigned long long q_full;
     unsigned long long k_full[AT_STAGES], k_empty[AT_STAGES];
@@ -147,23 +161,31 @@ struct AtParams {
     int n_q_heads, n_kv_heads, page_size;
     float scale_log2;
     int* error_word;
+    long long* trace;           // only read when compiled with AT_TRACE
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, (AT_N == 64) ? 2 : 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                AtParams p, const int4* __restrict__ tile_info) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // swizzled operand tiles need 1024-byte alignment; the declaration asks for it and a misaligned
+    // window is refused below rather than padded, so that two blocks fit the SM's shared memory
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* base = smem_raw;
+    if ((at_smem(base) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(p.error_word, 31);
+        return;
+    }
     unsigned char* sQ = base;                               // [2 slabs]
-    unsigned char* sK = sQ + AT_TILE;                       // [stages][2 slabs]
+    unsigned char* sK = sQ + AT_QTILE;                      // [stages][2 slabs]
     unsigned char* sV = sK + AT_STAGES * AT_TILE;           // [stages][2 slabs]
-    unsigned char* sP = sV + AT_STAGES * AT_TILE;           // [2 slabs]: keys 0..63, 64..127
-    AtShared* sh = reinterpret_cast<AtShared*>(sP + AT_TILE);
+    unsigned char* sP = sV + AT_STAGES * AT_TILE;           // [keys / 64 slabs]: keys 0..63, 64..127
+    AtShared* sh = reinterpret_cast<AtShared*>(sP + AT_PTILE);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.y;
+    // heads vary fastest, so all heads of the longest tile start first (tiles come sorted, longest first)
+    const int head = blockIdx.x;
     const int kv_head = head / (p.n_q_heads / p.n_kv_heads);
     // tile_info: (first token in the flat batch, its absolute position, 128, block-table row)
-    const int4 info = tile_info[blockIdx.x];
+    const int4 info = tile_info[blockIdx.y];
     const int n0 = info.x, pos0 = info.y;
     const int hi = pos0 + AT_M - 1;                          // last key any row of the tile may see
     const int n_tiles = hi / AT_N + 1;
@@ -182,51 +204,73 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(at_smem(&sh->tmem_base)), "r"(512u) : "memory");
+                     ::"r"(at_smem(&sh->tmem_base)), "r"((unsigned)AT_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     at_fence_before();
     __syncthreads();
     at_fence_after();
     const unsigned tmem = sh->tmem_base;
-    const unsigned tmem_s[2] = {tmem, tmem + 128u};
-    const unsigned tmem_o = tmem + 256u;
+    const unsigned tmem_s[2] = {tmem, tmem + (unsigned)AT_N};
+    const unsigned tmem_o = tmem + 2u * AT_N;
 
     if (warp == 0) {
+        // The whole warp walks the tiles: every lane fetches one block-table entry of a batch of 32 in one
+        // coalesced read, lane 0 waits, arms the barriers and issues the copies with ids handed over by
+        // shuffles (a dependent table read per page would cost the producer more than a tile's MMAs).
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_q) : "memory");
             asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_kv) : "memory");
             // queries: box (64 elements, 1 head, 128 tokens) per half of the head
-            at_expect_tx(&sh->q_full, AT_TILE);
+            at_expect_tx(&sh->q_full, AT_QTILE);
             at_tma_3d(sQ, &map_q, &sh->q_full, 0, head, n0);
-            at_tma_3d(sQ + AT_SLAB, &map_q, &sh->q_full, 64, head, n0);
-            const int pages_per_tile = AT_N / p.page_size;
-            const int page_bytes = p.page_size * 128;       // one page of one half: page_size rows of 128 bytes
-            bool ok = true;
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int stage = j % AT_STAGES;
-                const unsigned parity = ((j / AT_STAGES) & 1) ^ 1;
-                // pages of this tile that exist (positions up to hi); the others are never read unmasked
-                const int first_key = j * AT_N;
-                int pages = pages_per_tile;
-                if (first_key + AT_N - 1 > hi) pages = (hi - first_key) / p.page_size + 1;
-                for (int kv = 0; kv < 2 && ok; ++kv) {
-                    unsigned long long* full = kv == 0 ? &sh->k_full[stage] : &sh->v_full[stage];
-                    unsigned long long* empty = kv == 0 ? &sh->k_empty[stage] : &sh->v_empty[stage];
-                    unsigned char* dst = (kv == 0 ? sK : sV) + stage * AT_TILE;
-                    if (!at_wait(empty, parity)) { atomicExch(p.error_word, 11); ok = false; break; }
-                    at_expect_tx(full, (unsigned)(pages * 2 * page_bytes));
-                    for (int pg = 0; pg < pages; ++pg) {
-                        const int page = table[first_key / p.page_size + pg];
-                        // cache rows of one layer: ((page * 2 + kv) * kv_heads + kv_head) * page_size + slot
-                        const int row = ((page * 2 + kv) * p.n_kv_heads + kv_head) * p.page_size;
-                        at_tma_2d(dst + pg * page_bytes, &map_kv, full, 0, row);
-                        at_tma_2d(dst + AT_SLAB + pg * page_bytes, &map_kv, full, 64, row);
+            at_tma_3d(sQ + AT_QSLAB, &map_q, &sh->q_full, 64, head, n0);
+        }
+        const int pages_per_tile = AT_N / p.page_size;
+        const int tiles_per_batch = 32 / pages_per_tile;       // pages_per_tile is 1, 2, 4 or 8
+        const int page_bytes = p.page_size * 128;               // one page of one half: page_size rows of 128 bytes
+        const int last_page = hi / p.page_size;
+        int ok = 1;
+        int my_page = -1;
+        for (int j = 0; j < n_tiles; ++j) {
+            if (j % tiles_per_batch == 0) {
+                const int index = j * pages_per_tile + lane;
+                my_page = index <= last_page ? table[index] : -1;
+            }
+            const int stage = j % AT_STAGES;
+            const unsigned parity = ((j / AT_STAGES) & 1) ^ 1;
+            const int first_key = j * AT_N;
+            int pages = pages_per_tile;
+            if (first_key + AT_N - 1 > hi) pages = (hi - first_key) / p.page_size + 1;
+            // one copy per lane: lane = (half of the head, page of the tile).  Keys first: their stage is free
+            // as soon as the scores of two tiles ago are computed, long before the values' stage, and the
+            // next scores need them first.  (Issuing a tile's copies from one thread one after the other
+            // costs that thread more than the tile's MMAs take.)
+            const int pg = lane % pages_per_tile, half = (lane / pages_per_tile) & 1;
+            const int page = __shfl_sync(0xffffffffu, my_page, (j % tiles_per_batch) * pages_per_tile + pg);
+            for (int kv = 0; kv < 2; ++kv) {
+                if (lane == 0 && ok) {
+                    if (!at_wait(kv == 0 ? &sh->k_empty[stage] : &sh->v_empty[stage], parity)) {
+                        atomicExch(p.error_word, 11);
+                        ok = 0;
+                    } else {
+                        at_expect_tx(kv == 0 ? &sh->k_full[stage] : &sh->v_full[stage], (unsigned)(pages * 2 * page_bytes));
                     }
                 }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (ok && lane < 2 * pages_per_tile && pg < pages) {
+                    // cache rows of one layer: ((page * 2 + kv) * kv_heads + kv_head) * page_size + slot
+                    const int row = ((page * 2 + kv) * p.n_kv_heads + kv_head) * p.page_size;
+                    unsigned char* dst = (kv == 0 ? sK : sV) + stage * AT_TILE + half * AT_SLAB + pg * page_bytes;
+                    at_tma_2d(dst, &map_kv, kv == 0 ? &sh->k_full[stage] : &sh->v_full[stage], half * 64, row);
+                }
+                if (lane == 0) AT_STAMP(0, 2 * j + kv);
             }
-            // leave only after the copies have been consumed or have had a second to land
-            for (int j = n_tiles; j < n_tiles + AT_STAGES && ok; ++j) {
+            if (!ok) break;
+        }
+        // leave only after the copies have been consumed or have had a second to land
+        if (lane == 0 && ok) {
+            for (int j = n_tiles; j < n_tiles + AT_STAGES; ++j) {
                 const int stage = j % AT_STAGES;
                 const unsigned parity = ((j / AT_STAGES) & 1) ^ 1;
                 if (!at_wait(&sh->k_empty[stage], parity) || !at_wait(&sh->v_empty[stage], parity)) {
@@ -237,9 +281,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // both MMAs: M = 128, N = 128, bfloat16 -> float32; the second one reads B (V) MN-major
+            // bfloat16 -> float32, M = 128; scores: N = keys; output: N = head size, B (V) read MN-major
             const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_N >> 3) << 17) | ((unsigned)(AT_M >> 4) << 24);
-            const unsigned idesc_pv = idesc_s | (1u << 16);
+            const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(AT_D >> 3) << 17) | ((unsigned)(AT_M >> 4) << 24);
             bool ok = at_wait(&sh->q_full, 0);
             if (!ok) atomicExch(p.error_word, 13);
             auto issue_scores = [&](int j) -> bool {
@@ -250,11 +294,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 const unsigned q_addr = at_smem(sQ), k_addr = at_smem(sK + stage * AT_TILE);
 #pragma unroll
                 for (int kk = 0; kk < AT_D / 16; ++kk) {
-                    const unsigned off = (kk >> 2) * AT_SLAB + (kk & 3) * 32;      // half of the head, then 16 elements = 32 bytes
-                    at_mma(tmem_s[buf], at_desc_kmajor(q_addr + off), at_desc_kmajor(k_addr + off), idesc_s, kk ? 1u : 0u);
+                    // half of the head, then 16 elements = 32 bytes inside the 128-byte row
+                    at_mma(tmem_s[buf], at_desc_kmajor(q_addr + (kk >> 2) * AT_QSLAB + (kk & 3) * 32),
+                           at_desc_kmajor(k_addr + (kk >> 2) * AT_SLAB + (kk & 3) * 32), idesc_s, kk ? 1u : 0u);
                 }
                 at_commit(&sh->s_full[buf]);
                 at_commit(&sh->k_empty[stage]);
+                AT_STAMP(1, 4 * j);
                 return true;
             };
             if (ok) ok = issue_scores(0);
@@ -262,18 +308,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (j + 1 < n_tiles) { ok = issue_scores(j + 1); if (!ok) break; }
                 const int stage = j % AT_STAGES;
                 if (!at_wait(&sh->v_full[stage], (j / AT_STAGES) & 1)) { atomicExch(p.error_word, 16); ok = false; break; }
+                AT_STAMP(1, 4 * j + 1);
                 if (!at_wait(&sh->p_full, j & 1)) { atomicExch(p.error_word, 17); ok = false; break; }
+                AT_STAMP(1, 4 * j + 2);
                 at_fence_after();
                 const unsigned p_addr = at_smem(sP), v_addr = at_smem(sV + stage * AT_TILE);
 #pragma unroll
                 for (int kk = 0; kk < AT_N / 16; ++kk) {
                     // P: 16 keys = 32 bytes inside the key half; V: 16 keys = 16 rows of 128 bytes
-                    const unsigned p_off = (kk >> 2) * AT_SLAB + (kk & 3) * 32;
+                    const unsigned p_off = (kk >> 2) * AT_QSLAB + (kk & 3) * 32;
                     at_mma(tmem_o, at_desc_kmajor(p_addr + p_off), at_desc_mnmajor(v_addr + kk * 2048), idesc_pv,
                            (j | kk) ? 1u : 0u);
                 }
                 at_commit(&sh->pv_done);
                 at_commit(&sh->v_empty[stage]);
+                AT_STAMP(1, 4 * j + 3);
             }
         }
     } else {
@@ -285,20 +334,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int buf = j & 1, stage = j % AT_STAGES;
+            if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j);
             if (!at_wait(&sh->s_full[buf], (j >> 1) & 1)) { if (lane == 0) atomicExch(p.error_word, 21); ok = false; break; }
+            if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j + 1);
             at_fence_after();
             float s[AT_N];
+            {
+                unsigned r[AT_N / 32][32];
 #pragma unroll
-            for (int c = 0; c < AT_N / 32; ++c) {
-                unsigned r[32];
-                at_tmem_ld32(tmem_s[buf] + lane_base + c * 32, r);
-                at_wait_ld();
+                for (int c = 0; c < AT_N / 32; ++c) at_tmem_ld32(tmem_s[buf] + lane_base + c * 32, r[c]);
+                at_wait_ld();                                  // one wait for all the loads
 #pragma unroll
-                for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
+                for (int c = 0; c < AT_N / 32; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[c][i]);
             }
             at_fence_before();
             __syncwarp();
             if (lane == 0) at_arrive(&sh->s_empty[buf]);      // the score buffer may be overwritten
+            if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j + 2);
             // scale, mask by absolute position (only tiles that reach past the first row's position need it)
             const int key0 = j * AT_N;
             float tmax = -INFINITY;
@@ -312,14 +366,31 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     tmax = fmaxf(tmax, s[i]);
                 }
             }
-            // O is stable and P's buffer free once the previous tile's second MMA is done
-            if (j > 0 && !at_wait(&sh->pv_done, (j - 1) & 1)) { if (lane == 0) atomicExch(p.error_word, 22); ok = false; break; }
-            at_fence_after();
             // Move the maximum only when it grew by more than 2^8: until then exp2(s - m_used) <= 256,
             // harmless in float32 and bfloat16, and O needs no rescale (which costs a TMEM round trip).
             const bool grow = tmax > m_used + 8.0f;            // also true at the first tile (m_used = -inf)
-            if (__any_sync(0xffffffffu, grow && j > 0)) {
-                const float factor = grow ? at_exp2(m_used - tmax) : 1.0f;     // exp2(-inf) = 0 cannot occur for j > 0 rows with keys
+            const float factor = (grow && j > 0) ? at_exp2(m_used - tmax) : 1.0f;
+            if (grow) m_used = tmax;
+            const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+            // P = exp2(s - m) as bfloat16, kept in registers until the buffer is free
+            float sum = 0.f;
+            uint4 packed[AT_N / 8];
+#pragma unroll
+            for (int c = 0; c < AT_N / 8; ++c) {
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { e[i] = at_exp2(s[c * 8 + i] - m_safe); sum += e[i]; }
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(e[0], e[1]), b1 = __floats2bfloat162_rn(e[2], e[3]);
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(e[4], e[5]), b3 = __floats2bfloat162_rn(e[6], e[7]);
+                packed[c].x = *reinterpret_cast<unsigned*>(&b0); packed[c].y = *reinterpret_cast<unsigned*>(&b1);
+                packed[c].z = *reinterpret_cast<unsigned*>(&b2); packed[c].w = *reinterpret_cast<unsigned*>(&b3);
+            }
+            // O is stable and P's buffer free once the previous tile's second MMA is done
+            if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j + 3);
+            if (j > 0 && !at_wait(&sh->pv_done, (j - 1) & 1)) { if (lane == 0) atomicExch(p.error_word, 22); ok = false; break; }
+            if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j + 4);
+            at_fence_after();
+            if (__any_sync(0xffffffffu, factor != 1.0f)) {
 #pragma unroll 1
                 for (int c = 0; c < AT_D / 32; ++c) {
                     unsigned r[32];
@@ -330,17 +401,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     at_tmem_st32(tmem_o + lane_base + c * 32, r);
                 }
                 at_wait_st();
-                if (grow) l *= factor;
-            } else if (grow && j == 0) {
-                // nothing accumulated yet
             }
-            if (grow) m_used = tmax;
-            const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+            l = l * factor + sum;
             // on the last tile, value rows past the last visible key may hold anything (unwritten slots):
             // zero them so that 0 * garbage cannot become NaN; they are this thread's key row
             if (j == n_tiles - 1) {
                 if (!at_wait(&sh->v_full[stage], (j / AT_STAGES) & 1)) { if (lane == 0) atomicExch(p.error_word, 23); ok = false; break; }
-                if (key0 + row > hi) {
+                if (row < AT_N && key0 + row > hi) {
                     unsigned char* v_row = sV + stage * AT_TILE + row * 128;
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
@@ -349,29 +416,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     }
                 }
             }
-            // P = exp2(s - m) as bfloat16 into the K-major operand image: row `row`, 16-byte chunk c of each
-            // 128-byte half-row goes to chunk (c ^ (row & 7))
-            float sum = 0.f;
+            // P into the K-major operand image: row `row`, 16-byte chunk c of each 128-byte half-row goes to
+            // chunk (c ^ (row & 7))
             unsigned char* p_row = sP + row * 128;
 #pragma unroll
             for (int c = 0; c < AT_N / 8; ++c) {
-                float e[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) { e[i] = at_exp2(s[c * 8 + i] - m_safe); sum += e[i]; }
-                uint4 packed;
-                __nv_bfloat162 b0 = __floats2bfloat162_rn(e[0], e[1]), b1 = __floats2bfloat162_rn(e[2], e[3]);
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(e[4], e[5]), b3 = __floats2bfloat162_rn(e[6], e[7]);
-                packed.x = *reinterpret_cast<unsigned*>(&b0); packed.y = *reinterpret_cast<unsigned*>(&b1);
-                packed.z = *reinterpret_cast<unsigned*>(&b2); packed.w = *reinterpret_cast<unsigned*>(&b3);
                 const int half = c >> 3, chunk = c & 7;
-                *reinterpret_cast<uint4*>(p_row + half * AT_SLAB + ((chunk ^ (row & 7)) << 4)) = packed;
+                *reinterpret_cast<uint4*>(p_row + half * AT_QSLAB + ((chunk ^ (row & 7)) << 4)) = packed[c];
             }
-            l += sum;
             // make the shared-memory writes visible to the tensor core's reads, and order the TMEM stores
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             at_fence_before();
             __syncwarp();
             if (lane == 0) at_arrive(&sh->p_full);
+            if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j + 5);
         }
         if (ok) {
             if (!at_wait(&sh->pv_done, (n_tiles - 1) & 1)) { if (lane == 0) atomicExch(p.error_word, 24); ok = false; }
@@ -401,7 +459,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     __syncthreads();
     if (warp == 1) {
         at_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((unsigned)AT_TMEM_COLS) : "memory");
     }
 }
 
@@ -422,19 +480,21 @@ static AtEncodeFn at_encode() {
 }
 
 extern "C" int qil_attn_tc_head_dim() { return AT_D; }
+extern "C" int qil_attn_tc_keys_per_tile() { return AT_N; }
 
 // q [N, Hq, 128], kv one layer's pages [pages, 2, Hkv, page_size, 128], out [N, Hq, 128], all bfloat16.
 // tile_info int32 [n_tiles, 4] = (first token, its absolute position, 128, block-table row): whole tiles only.
-// page_size must divide 128 and be a multiple of 8.  error_word: a device int, zeroed by the caller once.
+// page_size must divide the keys per tile and be a multiple of 8.  error_word: a device int, zeroed by the
+// caller once.  trace: null, or 3 * 1024 int64 for the time stamps of block (0, 0) in a build with AT_TRACE.
 extern "C" int qil_attn_tc_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
                                    int n_tokens, const int* block_table, int table_stride, int n_q_heads,
                                    int n_kv_heads, int page_size, int num_pages, float scale, int* error_word,
-                                   cudaStream_t stream) {
+                                   long long* trace, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (n_kv_heads <= 0 || n_q_heads % n_kv_heads) QIL_REFUSE("attn_tc: %d query heads, %d kv heads", n_q_heads, n_kv_heads);
-    if (page_size < 8 || page_size > 128 || 128 % page_size || page_size % 8)
-        QIL_REFUSE("attn_tc: pages of %d positions; this kernel takes 8, 16, 32, 64 or 128", page_size);
-    if (n_q_heads > 65535) QIL_REFUSE("attn_tc: too many heads");
+    if (page_size < 8 || page_size > AT_N || AT_N % page_size || page_size % 8)
+        QIL_REFUSE("attn_tc: pages of %d positions; this kernel takes multiples of 8 that divide %d", page_size, AT_N);
+    if (n_tiles > 65535) QIL_REFUSE("attn_tc: %d tiles in one launch; at most 65535", n_tiles);
     if (((uintptr_t)q | (uintptr_t)kv | (uintptr_t)out | (uintptr_t)tile_info) & 15) QIL_REFUSE("attn_tc: operands must be 16-byte aligned");
     if (error_word == nullptr) QIL_REFUSE("attn_tc: needs an error word");
     AtEncodeFn encode = at_encode();
@@ -466,13 +526,14 @@ extern "C" int qil_attn_tc_prefill(const void* q, const void* kv, void* out, con
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.error_word = error_word;
-    const int smem = AT_TILE * (2 + 2 * AT_STAGES) + (int)sizeof(AtShared) + 1024;
+    p.trace = trace;
+    const int smem = AT_QTILE + 2 * AT_STAGES * AT_TILE + AT_PTILE + (int)sizeof(AtShared);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) QIL_REFUSE("attn_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    attn_tc_kernel<<<dim3(n_tiles, n_q_heads), 192, smem, stream>>>(map_q, map_kv, p, (const int4*)tile_info);
+    attn_tc_kernel<<<dim3(n_q_heads, n_tiles), 192, smem, stream>>>(map_q, map_kv, p, (const int4*)tile_info);
     QIL_CHECK_LAUNCH();
 }

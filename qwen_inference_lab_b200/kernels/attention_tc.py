@@ -28,10 +28,11 @@ def library():
 
 
 def supports(head_dim, page_size, window) -> bool:
-    return head_dim == HEAD_DIM and window == 0 and page_size in (8, 16, 32, 64, 128)
+    return head_dim == HEAD_DIM and window == 0 and page_size in (8, 16, 32, 64)
 
 
-def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, page_size, scale):
+def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, page_size, scale, trace=None,
+            lib=None):
     """q, out bfloat16 [N, Hq*128]; pages [num_pages, 2, Hkv, page_size, 128];
     tile_info int32 [n_tiles * 4] = (first token, its position, 128, block-table row)."""
     global _error_word
@@ -40,11 +41,11 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
         raise KernelError("attention_tc: shapes do not match the head counts")
     if _error_word is None:
         _error_word = torch.zeros(1, dtype=torch.int32, device=q.device)
-    lib = library()
+    lib = lib or library()
     _check(lib, lib.qil_attn_tc_prefill(
         _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), c_int(q.shape[0]), _p(block_table),
         c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]),
-        c_float(scale), _p(_error_word), _stream()), "attention (128-token tiles)")
+        c_float(scale), _p(_error_word), _p(trace), _stream()), "attention (128-token tiles)")
 
 
 def check() -> None:

@@ -415,7 +415,7 @@ TENSOR_MEMORY_ATTENTION_CASES = [
     (4, 2, [384, 200], [128, 72], 16),
     (8, 2, [1024, 133], [0, 5], 8),
     (4, 4, [700], [60], 64),
-    (6, 1, [2100, 300], [1972, 44], 128),
+    (6, 1, [2100, 300], [1972, 44], 32),
     (32, 8, [2048], [0], 16),
 ]
 
