@@ -300,8 +300,8 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     bf16* sK = sQ + 16 * LDS;                           // [2][64][LDS]
     bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
     int* s_pages = reinterpret_cast<int*>(sV + 2 * KV_TILE * LDS);   // [span_len / page_size + 2]
-    qil_wait_for_producer();
-    qil_release_consumer();
+    // Up to qil_wait_for_producer() below only memory that no kernel of this step writes is read:
+    // the step's description, the block table, and keys and values of earlier positions.
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = p.n_q_heads / p.n_kv_heads;
     const int chunks = (group + 15) / 16;
@@ -318,12 +318,6 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     const int first_tile = max(k_begin, lo) / KV_TILE;
     const int last_tile = min(k_begin + span_len - 1, hi) / KV_TILE;
 
-    {   // the query heads of this kv head: 8 threads per row
-        const int row = tid >> 3;
-        const bool valid = row < gcount;
-        const bf16* src = p.q + ((size_t)n * p.n_q_heads + kv_head * group + g0 + (valid ? row : 0)) * D;
-        for (int c = tid & 7; c < D / 8; c += 8) cp_async16(sQ + row * LDS + c * 8, src + c * 8, valid);
-    }
     // the page ids of the whole span, once: a tile's loads then wait for no table read
     const int first_page = (first_tile * KV_TILE) / p.page_size;
     const int last_page = min((last_tile + 1) * KV_TILE - 1, hi) / p.page_size;
@@ -336,7 +330,20 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
                                         min(hi, (last_tile + 1) * KV_TILE - 1));
     }
     __syncthreads();
-    issue_kv_tile(p, row_off[0], sK, sV, tid);
+    // The first tile starts before the wait unless it holds this step's own position, whose key and
+    // value the kernel before this one is still writing.
+    const bool early = first_tile != hi / KV_TILE;
+    if (early) issue_kv_tile(p, row_off[0], sK, sV, tid);
+    cp_async_commit();
+    qil_wait_for_producer();
+    qil_release_consumer();
+    {   // the query heads of this kv head: 8 threads per row
+        const int row = tid >> 3;
+        const bool valid = row < gcount;
+        const bf16* src = p.q + ((size_t)n * p.n_q_heads + kv_head * group + g0 + (valid ? row : 0)) * D;
+        for (int c = tid & 7; c < D / 8; c += 8) cp_async16(sQ + row * LDS + c * 8, src + c * 8, valid);
+    }
+    if (!early) issue_kv_tile(p, row_off[0], sK, sV, tid);
     cp_async_commit();
 
     unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];

@@ -54,6 +54,7 @@ class StepRunner:
         self._ring = PinnedRing() if self.device.type == "cuda" else None
         self._graphs: dict = {}
         self._graph_pool = None
+        self._extras: dict = {}      # what parts keep from step to step (scratch buffers), by their own keys
         self._reserve(8 * max_step_tokens + 16 * cache.max_requests + 64)
         self.steps_run = 0
         self.kernel_launches = 0          # this engine's own kernels (library products are not counted)
@@ -153,7 +154,7 @@ class StepRunner:
             n_big_tiles=offsets["big_tile_info"][1] // 4, big_tile_info=section("big_tile_info"),
             n_rest_tiles=offsets["rest_tile_info"][1] // 4, rest_tile_info=section("rest_tile_info"),
             max_context=max_context, h_seg_row=host["seg_row"], h_seg_start=host["seg_start"],
-            h_seg_len=host["seg_len"], h_seg_pos0=host["seg_pos0"])
+            h_seg_len=host["seg_len"], h_seg_pos0=host["seg_pos0"], extras=self._extras)
 
     def _upload(self, packed):
         self._reserve(len(packed))
@@ -239,10 +240,11 @@ class StepRunner:
                     current.capture_end()
                 graphs.append(current)
             torch.cuda.current_stream().wait_stream(stream)
-            record = (graphs, logits, ops.launch_count() - before)
+            # the graphs hold addresses of what the parts keep in ``extras`` (scratch): keep those alive
+            record = (graphs, logits, ops.launch_count() - before, dict(self._extras))
             self._graphs[key] = record
             self.launches_per_graph[n] = record[2]
-        graphs, logits, launches = record
+        graphs, logits, launches = record[:3]
         for graph in graphs:
             graph.replay()
         self.kernel_launches += launches

@@ -44,8 +44,8 @@ def choose_span(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> i
     Blocks run in waves of (SMs x blocks per SM); a wave takes about (tiles per span + 2) tile
     times, the 2 standing for a block's start-up (its metadata, page ids and first tile arrive one
     after the other); every further span also costs a little in the merge.  The span with the
-    lowest cost wins; measured on B200 at context 8192 this picks 640 for batch 8 (832 blocks,
-    two full waves: 56 us instead of 61 us at 512) and 2048 for batch 64.
+    lowest cost wins; measured on B200 at context 8192 this picks 1408 for batch 8 (384 blocks, one
+    wave: 54 us against 58-66 us for spans of 384 to 1024) and 1664 for batch 64.
     """
     global _sm_count
     if _sm_count is None:
@@ -66,13 +66,20 @@ def choose_span(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> i
 
 
 def decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim):
-    key = ("attn_decode_scratch", n_decode, n_q_heads, n_spans, head_dim)
-    scratch = ctx.extras.get(key)
-    if scratch is None:
-        slots = n_decode * n_q_heads * n_spans
-        scratch = (torch.empty(slots * head_dim, dtype=torch.float32, device=ctx.device),
-                   torch.empty(slots * 2, dtype=torch.float32, device=ctx.device))
-        ctx.extras[key] = scratch
+    """Partial sums and their (max, sum) pairs for the single-token kernel.
+
+    One pair of buffers per runner, kept in ``ctx.extras`` (which the runner carries from step to
+    step) and replaced by a larger pair when a step needs more; a recorded graph keeps the pair it
+    was recorded with alive.
+    """
+    slots = n_decode * n_q_heads * n_spans
+    scratch = ctx.extras.get("attn_decode_scratch")
+    if scratch is None or scratch[0].numel() < slots * head_dim or scratch[1].numel() < slots * 2:
+        grow = lambda old, need: max(need, 2 * old.numel() if old is not None else 0)
+        old = scratch or (None, None)
+        scratch = (torch.empty(grow(old[0], slots * head_dim), dtype=torch.float32, device=ctx.device),
+                   torch.empty(grow(old[1], slots * 2), dtype=torch.float32, device=ctx.device))
+        ctx.extras["attn_decode_scratch"] = scratch
     return scratch
 
 

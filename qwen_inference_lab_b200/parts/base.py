@@ -157,6 +157,7 @@ class StepContext:
     h_seg_start: object = None
     h_seg_len: object = None
     h_seg_pos0: object = None
+    # the runner's own dict, the same one every step: parts keep scratch buffers here under their own keys
     extras: dict = field(default_factory=dict)
 
     def empty(self, shape, dtype=None):
