@@ -67,6 +67,7 @@ class StepRunner:
         self._capacity = int(ints)
         self._meta_dev = torch.zeros(self._capacity, dtype=torch.int32, device=self.device)
         self._graphs.clear()     # recorded graphs point into the old buffer
+        self._graph_pool = None  # their memory pool goes with the last of them: the next recording starts a new one
 
     # ------------------------------------------------------------------ the batch
     def _validate(self, entries):

@@ -48,3 +48,26 @@ def test_replay_matches_plain(folders, case, schedule, dtype):
     expected = harness.plain_rows(requests, weights, cfg, torch.float32)
     yardstick = harness.plain_rows(requests, weights, cfg, dtype) if dtype == torch.bfloat16 else None
     harness.assert_rows_close(actual, expected, dtype, f"tiny {case} {schedule} {dtype}", yardstick)
+
+
+def test_recorded_steps_survive_a_step_that_outgrows_the_runner(folders):
+    """Single-token steps are recorded as graphs; a later step with more tokens than the runner was
+    made for replaces the buffers those graphs point into.  The recordings are then made anew, in a
+    new memory pool, and the scratch that the parts keep between steps stays valid."""
+    from qwen_inference_lab_b200.cache import CacheManager
+    from qwen_inference_lab_b200.engine import StepRunner
+    from qwen_inference_lab_b200.loading import load_model
+    folder, weights, _ = folders["B"]
+    cfg = CASES["B"]["cfg"]
+    model = load_model(folder, device="cuda", dtype=torch.bfloat16)
+    cache = CacheManager(model.cache_specs(), num_pages=64, page_size=8, max_requests=4,
+                         max_context=model.max_positions, dtype=torch.bfloat16, device=model.device)
+    cache.poison()
+    runner = StepRunner(model, cache, max_step_tokens=16)
+    requests = {"a": harness.random_tokens(cfg, 40, 1), "b": harness.random_tokens(cfg, 300, 2)}
+    schedule = harness.tail_decode_schedule(requests, tail=8)      # a: 32 + 8 x 1, then b: 292 + 8 x 1
+    actual = harness.run_schedule(runner, cache, schedule)
+    assert runner._graphs, "single-token steps should have been recorded"
+    expected = harness.plain_rows(requests, weights, cfg, torch.float32)
+    yardstick = harness.plain_rows(requests, weights, cfg, torch.bfloat16)
+    harness.assert_rows_close(actual, expected, torch.bfloat16, "after the buffers grew", yardstick)
