@@ -34,6 +34,12 @@ QWEN3_8B = dict(vocab_size=151936, hidden_size=4096, intermediate_size=12288, nu
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=40960,
                 rms_norm_eps=1e-6, rope_theta=1000000.0, attention_bias=False, tie_word_embeddings=False,
                 eos_token_id=None)
+QWEN3_32B = dict(QWEN3_8B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64)
+QWEN3_06B = dict(QWEN3_8B, hidden_size=1024, intermediate_size=3072, num_hidden_layers=28, num_attention_heads=16,
+                 tie_word_embeddings=True)
+# name -> (sizes, label, context of the decode measurements)
+SHAPES = {"8b": (QWEN3_8B, "Qwen3-8B shape", 8192), "32b": (QWEN3_32B, "Qwen3-32B shape", 8192),
+          "0.6b": (QWEN3_06B, "Qwen3-0.6B shape", 4096)}
 CONTEXT = 8192
 PAGE_SIZE = 16
 PREFILL_TOKENS = 2048
@@ -130,7 +136,7 @@ def prefill_flops(cfg, tokens, logit_rows=1):
 
 # --------------------------------------------------------------------------- our engine
 class OursBench:
-    def __init__(self, cfg, layers=None):
+    def __init__(self, cfg, layers=None, dtype="bfloat16"):
         import torch
         from qwen_inference_lab_b200.config import Qwen3Config
         from qwen_inference_lab_b200.loading import random_model
@@ -139,9 +145,18 @@ class OursBench:
         self.full_layers = cfg["num_hidden_layers"]
         if layers:
             self.cfg["num_hidden_layers"] = layers
+        self.dtype = getattr(torch, dtype)
         self.model = random_model(Qwen3Config.from_dict(dict(self.cfg, model_type="qwen3")), seed=0,
-                                  device="cuda", dtype=torch.bfloat16)
+                                  device="cuda", dtype=self.dtype)
         torch.cuda.synchronize()
+
+    def largest_context(self, batch, wanted, reserve=6 << 30):
+        """The longest context (a multiple of 1024, at most ``wanted``) whose cache for ``batch`` requests fits."""
+        free, _ = self.torch.cuda.mem_get_info()
+        per_token = (self.cfg["num_hidden_layers"] * 2 * self.cfg["num_key_value_heads"] * self.cfg["head_dim"]
+                     * self.dtype.itemsize)
+        fits = int((free - reserve) // (batch * per_token)) // 1024 * 1024
+        return max(1024, min(wanted, fits))
 
     def _fill_cache(self, cache, ids, context):
         for g in cache.kv_groups:
@@ -160,7 +175,7 @@ class OursBench:
         total = context + steps + warmup + 2
         pages_per_request = (total + PAGE_SIZE - 1) // PAGE_SIZE
         cache = CacheManager(self.model.cache_specs(), num_pages=batch * pages_per_request, page_size=PAGE_SIZE,
-                             max_requests=batch, max_context=pages_per_request * PAGE_SIZE, dtype=torch.bfloat16,
+                             max_requests=batch, max_context=pages_per_request * PAGE_SIZE, dtype=self.dtype,
                              device=self.model.device)
         runner = StepRunner(self.model, cache, max_step_tokens=max(batch, 64))
         ids = list(range(batch))
@@ -189,7 +204,7 @@ class OursBench:
         assert torch.isfinite(logits).all()
         per_step = getattr(runner, "launches_per_graph", {}).get(batch)
         result = dict(ms_per_step=ms, tokens_per_s=batch / ms * 1e3,
-                      bytes=decode_bytes(self.cfg, batch, context + warmup + steps // 2),
+                      bytes=decode_bytes(self.cfg, batch, context + warmup + steps // 2, self.dtype.itemsize),
                       launches=per_step * steps if per_step else ops.launch_count() - launches_before,
                       clocks=sampler.summary() if sampler else None)
         del runner, cache
@@ -202,7 +217,7 @@ class OursBench:
         from qwen_inference_lab_b200.engine import StepEntry, StepRunner
         pages = (tokens_n + PAGE_SIZE - 1) // PAGE_SIZE + 1
         cache = CacheManager(self.model.cache_specs(), num_pages=pages, page_size=PAGE_SIZE, max_requests=2,
-                             max_context=pages * PAGE_SIZE, dtype=torch.bfloat16, device=self.model.device)
+                             max_context=pages * PAGE_SIZE, dtype=self.dtype, device=self.model.device)
         runner = StepRunner(self.model, cache, max_step_tokens=tokens_n)
         generator = torch.Generator().manual_seed(2)
         prompt = torch.randint(0, self.cfg["vocab_size"], (tokens_n,), generator=generator).tolist()
@@ -263,12 +278,41 @@ class OursBench:
                     ms_per_step=elapsed / steps * 1e3)
 
 
+def mixed_workload(bench, requests=64, new_tokens=128, longest=2048, seed=4):
+    """Requests with prompts of 16 to ``longest`` tokens (uniform, seeded), ``new_tokens`` each, all
+    submitted at once to ``Engine.generate``: output tokens per second of the whole run, wall clock."""
+    import torch
+    from qwen_inference_lab_b200 import Engine
+    generator = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(16, longest + 1, (requests,), generator=generator).tolist()
+    prompts = [torch.randint(0, bench.cfg["vocab_size"], (n,), generator=generator).tolist() for n in lengths]
+    pages = sum((n + new_tokens + PAGE_SIZE - 1) // PAGE_SIZE + 1 for n in lengths)
+    engine = Engine(bench.model, num_pages=pages, page_size=PAGE_SIZE, token_budget=4096, prefill_chunk=2048,
+                    max_active=requests)
+    engine.generate(prompts[:2], max_new_tokens=4, ignore_eos=True)        # set-up outside the timed run
+    torch.cuda.synchronize()
+    steps_before = engine.runner.steps_run
+    begin = time.perf_counter()
+    rows = engine.generate(prompts, max_new_tokens=new_tokens, ignore_eos=True)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - begin
+    produced = sum(len(row["token_ids"]) for row in rows)
+    steps = engine.runner.steps_run - steps_before
+    engine.close()
+    return {"value": round(produced / elapsed, 1), "unit": "output tokens/s", "requests": requests,
+            "prompt_tokens": sum(lengths), "new_tokens": produced, "steps": steps, "seconds": round(elapsed, 3)}
+
+
 def run_ours(args):
     import torch
     pk = peaks()
-    bench = OursBench(QWEN3_8B, layers=args.layers)
+    sizes, label, context = SHAPES[args.shape]
+    bench = OursBench(sizes, layers=args.layers, dtype=args.dtype)
     cfg = bench.cfg
     batch = args.batch
+    if args.only == "mixed":
+        print(json.dumps({"workload": "mixed", "model": label, "dtype": args.dtype, **mixed_workload(bench)}))
+        return
     if args.only == "decode":
         part = bench.decode(batch, args.context, args.steps, args.warmup)
         print(f"decode batch {batch} context {args.context} layers {cfg['num_hidden_layers']}: {part['ms_per_step']:.3f} ms/step")
@@ -277,35 +321,39 @@ def run_ours(args):
         ms = bench.prefill(PREFILL_TOKENS, reps=args.steps if args.steps != 32 else 2, warmup=3)
         print(f"prefill {PREFILL_TOKENS} tokens layers {cfg['num_hidden_layers']}: {ms:.3f} ms (all: {bench.last_prefill_times})")
         return
-    main = bench.decode(batch, CONTEXT, args.steps, args.warmup, sample_clocks=True)
+    main = bench.decode(batch, context, args.steps, args.warmup, sample_clocks=True)
     points = {}
     for b in (1, 64):
         if args.quick:
             break
-        points[f"decode_b{b}"] = round(bench.decode(b, CONTEXT, max(8, args.steps // 2), args.warmup)["tokens_per_s"], 1)
+        fits = bench.largest_context(b, context)      # the 32B shape holds 64 requests only at a shorter context
+        key = f"decode_b{b}" if fits == context else f"decode_b{b}_context{fits}"
+        points[key] = round(bench.decode(b, fits, max(8, args.steps // 2), args.warmup)["tokens_per_s"], 1)
     prefill_ms = bench.prefill(PREFILL_TOKENS)
-    e2e = bench.e2e(batch, CONTEXT, args.steps, args.warmup)
+    e2e = bench.e2e(batch, context, args.steps, args.warmup)
     flops = prefill_flops(cfg, PREFILL_TOKENS)
     achieved = main["bytes"] / (main["ms_per_step"] * 1e-3) / 1e9
     of = "of measured" if pk["source"] == "measured" else "of fallback"
     line = {
-        "metric": "decode tokens/s (Qwen3-8B shape, batch 8, context 8192)",
+        "metric": f"decode tokens/s ({label}, batch {batch}, context {context})",
         "value": round(main["tokens_per_s"], 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights, random token ids, random cache contents",
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic: random weights, random token ids, random cache contents",
         "impl": "ours",
-        "config": {"model": "Qwen3-8B shape", "layers": cfg["num_hidden_layers"], "layers_of_config": bench.full_layers,
+        "config": {"model": label, "layers": cfg["num_hidden_layers"], "layers_of_config": bench.full_layers,
                    "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "tied": False,
-                   "global_batch": batch, "seq_len": CONTEXT, "page_size": PAGE_SIZE, "parallelism": "single GPU",
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "tied": cfg["tie_word_embeddings"],
+                   "global_batch": batch, "seq_len": context, "page_size": PAGE_SIZE, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (decode reads >16 GB per step); prefill flushes a 256 MB buffer",
                    "peaks": of},
         "clocks": main["clocks"],
         "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": int(main["launches"]),
         "prefill": {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
-                    "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "ms": round(prefill_ms, 3),
+                    # the peak is the bfloat16 tensor-core one: no fraction for the float32 check path
+                    "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4) if args.dtype == "bfloat16" else None,
                     "ms_min": bench.last_prefill_times[0], "ms_max": bench.last_prefill_times[-1],
                     "sm_mhz": bench.last_prefill_clocks["sm_mhz"], "reasons": bench.last_prefill_clocks["reasons"]},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -395,8 +443,11 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     parser.add_argument("--quick", action="store_true", help="skip the batch 1 and 64 points")
-    parser.add_argument("--only", choices=["decode", "prefill"], default=None,
-                        help="profiling aid: run just this part and print its time instead of the JSON line")
+    parser.add_argument("--only", choices=["decode", "prefill", "mixed"], default=None,
+                        help="run just this part and print its result instead of the JSON line; mixed = 64 requests "
+                             "with prompts of 16 to 2048 tokens and 128 new tokens each through Engine.generate")
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes (default: Qwen3-8B)")
+    parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     parser.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per request (profiling aid)")
     args = parser.parse_args()
     if args.gpus != 1:
