@@ -3,7 +3,8 @@ to the framework's files.  It is a toy, not anyone's model.  Its layers differ i
 
   0  a mixer with a state of its own (a decaying running sum kept in a per-request slot)
   1  full attention with q/k norms and full rotation
-  2  attention with a window of 20 positions and rotation of half of each head only
+  2  attention with a window of 20 positions and rotation of half of each head only; its feed-forward is
+     routed: a float32 router picks two of three small experts per token
   3  attention without k/v projections that reads the pages layer 1 wrote
 
 and its order names layer 0 twice: [0, 1, 2, 3, 0].  Each call of layer 0 keeps its own state.
@@ -34,6 +35,9 @@ class ToyConfig:
     theta: float = 10000.0
     eps: float = 1e-5
     inner: int = 72
+    experts: int = 3
+    experts_per_token: int = 2
+    expert_inner: int = 40
     max_positions: int = 512
 
     architecture = "ToyStateLM"
@@ -48,7 +52,39 @@ class ToyConfig:
 
 
 def make_parts():
-    from qwen_inference_lab_b200.parts import Mixer, Param, StateSpec
+    from qwen_inference_lab_b200.parts import FeedForward, Mixer, Param, StateSpec
+
+    class RoutedFeedForward(FeedForward):
+        """Router logits in float32, softmax over the chosen experts, tokens gathered per expert and
+        put back in their order before the residual is added."""
+
+        def __init__(self, width, inner, experts, per_token, *, name):
+            self.per_token, self.name = per_token, name
+            self.router = Param((experts, width), std=0.5)
+            self.gate = [Param((inner, width), std=0.1) for _ in range(experts)]
+            self.up = [Param((inner, width), std=0.1) for _ in range(experts)]
+            self.down = [Param((width, inner), std=0.1) for _ in range(experts)]
+
+        def named_params(self):
+            names = {self.name + ".router": self.router}
+            for e, (g, u, d) in enumerate(zip(self.gate, self.up, self.down)):
+                names.update({f"{self.name}.experts.{e}.gate": g, f"{self.name}.experts.{e}.up": u,
+                              f"{self.name}.experts.{e}.down": d})
+            return names
+
+        def forward(self, ctx, x, residual=None):
+            logits = x.float() @ self.router.data.float().t()
+            top, chosen = logits.topk(self.per_token, dim=-1)
+            weights = torch.softmax(top, dim=-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for e in range(len(self.gate)):
+                token, slot = (chosen == e).nonzero(as_tuple=True)
+                if token.numel() == 0:
+                    continue
+                xe = x[token].float()
+                hidden = torch.nn.functional.silu(xe @ self.gate[e].data.float().t()) * (xe @ self.up[e].data.float().t())
+                out.index_add_(0, token, (hidden @ self.down[e].data.float().t()) * weights[token, slot].unsqueeze(1))
+            return (out if residual is None else residual.float() + out).to(x.dtype)
 
     class RunningStateMixer(Mixer):
         """h_t = decay * h_{t-1} + W_in x_t ;  y_t = W_out h_t.  The state h lives in the request's slot."""
@@ -76,18 +112,20 @@ def make_parts():
             y = (h_all @ self.w_out.data.float().t()).to(x.dtype)
             return y if residual is None else (residual.float() + y.float()).to(x.dtype)
 
-    return RunningStateMixer
+    return RunningStateMixer, RoutedFeedForward
 
 
 def build_toy(config):
     from qwen_inference_lab_b200.parts import (DecoderModel, GatedMLP, GroupedQueryAttention, LayerCall, Linear,
                                                PreNormBlock, RMSNorm, RotaryEmbedding, TokenEmbedding)
-    RunningStateMixer = make_parts()
+    RunningStateMixer, RoutedFeedForward = make_parts()
     w, d = config.width, config.head_dim
-    def block(i, mixer):
+    def block(i, mixer, routed=False):
+        feed_forward = RoutedFeedForward(w, config.expert_inner, config.experts, config.experts_per_token,
+                                         name=f"blocks.{i}.ff") if routed else \
+            GatedMLP(w, config.inner, names={k: f"blocks.{i}.ff.{k}" for k in ("gate", "up", "down")})
         return PreNormBlock(RMSNorm(w, config.eps, name=f"blocks.{i}.norm_a"), mixer,
-                            RMSNorm(w, config.eps, name=f"blocks.{i}.norm_b"),
-                            GatedMLP(w, config.inner, names={k: f"blocks.{i}.ff.{k}" for k in ("gate", "up", "down")}))
+                            RMSNorm(w, config.eps, name=f"blocks.{i}.norm_b"), feed_forward)
     def attention(i, **kw):
         names = {k: f"blocks.{i}.attn.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
         return GroupedQueryAttention(w, config.heads, config.kv_heads, d, names=names, **kw)
@@ -95,7 +133,8 @@ def build_toy(config):
         block(0, RunningStateMixer(w, config.state_width, config.decay, name="blocks.0.state")),
         block(1, attention(1, qk_norm_eps=config.eps, position=RotaryEmbedding(d, config.theta, config.max_positions))),
         block(2, attention(2, qk_norm_eps=config.eps, window=config.window, bias=True,
-                           position=RotaryEmbedding(config.partial_rotary, config.theta, config.max_positions))),
+                           position=RotaryEmbedding(config.partial_rotary, config.theta, config.max_positions)),
+              routed=True),
         block(3, attention(3, reads_shared_cache=True, position=RotaryEmbedding(d, config.theta, config.max_positions))),
     ]
     embedding = TokenEmbedding(config.vocab_size, w, name="embed")
@@ -113,7 +152,22 @@ def toy_plain_logits(tokens, w, c: ToyConfig):
     positions = torch.arange(T)
     kv_of_layer1 = {}
 
+    def routed_ff(i, x):
+        n = plain.rms_norm(x, w[f"blocks.{i}.norm_b.weight"], c.eps)
+        logits = n @ w[f"blocks.{i}.ff.router"].t()
+        out = torch.zeros_like(x)
+        for t in range(T):                      # one token at a time: the plainest form
+            top, chosen = logits[t].topk(c.experts_per_token)
+            share = torch.softmax(top, dim=-1)
+            for e, p in zip(chosen.tolist(), share):
+                pre = f"blocks.{i}.ff.experts.{e}."
+                hidden = torch.nn.functional.silu(n[t] @ w[pre + "gate"].t()) * (n[t] @ w[pre + "up"].t())
+                out[t] += p * (hidden @ w[pre + "down"].t())
+        return x + out
+
     def ff(i, x):
+        if i == 2:
+            return routed_ff(i, x)
         n = plain.rms_norm(x, w[f"blocks.{i}.norm_b.weight"], c.eps)
         gate = torch.nn.functional.silu(plain.linear(n, w[f"blocks.{i}.ff.gate.weight"]))
         return x + plain.linear(gate * plain.linear(n, w[f"blocks.{i}.ff.up.weight"]), w[f"blocks.{i}.ff.down.weight"])
@@ -195,6 +249,7 @@ def test_toy_is_registered_built_and_loaded(toy):
     assert len(cache.state_groups) == 1 and cache.state_groups[0][1] == [0, 4]      # layer 0 twice: two states
     assert [g.spec.window for g in cache.kv_groups] == [0, 20] and cache.specs[3] is None
     assert "blocks.3.attn.k.weight" not in weights and "blocks.0.state.w_in" in weights
+    assert "blocks.2.ff.experts.2.down" in weights and "blocks.2.ff.gate.weight" not in weights
 
 
 @pytest.mark.parametrize("schedule", ["whole", "tail_decode", "chunks", "mixed"])
