@@ -15,6 +15,13 @@
 // warps of a block split every stage's k-range; their partial sums are added in
 // shared memory in warp order, so the result is deterministic.
 //
+// With a norm weight the kernel also does the RMSNorm that precedes the product
+// (qil/model.py:21-23,30-31): x arrives un-normed, each element is multiplied by the
+// norm weight on its way into the MMA (one bfloat16 rounding), the squares of x are
+// summed in float32 alongside (as the diagonal of X X^T, two more MMAs per 32 k-values),
+// and the accumulators are scaled by rsqrt(mean(x^2) + eps) in the epilogue.  The norm weight rides through the ring as
+// one more stage row.
+//
 // Epilogues: bias, residual (may alias out), float32 output for the LM head,
 // and `silu_pairs`: weight rows stored as groups of [8 gate rows, 8 up rows], for
 // which the block writes silu(gate) * up, 8 values per token
@@ -22,7 +29,12 @@
 #include "common.cuh"
 
 #define GSM_ROWS 16
+#ifndef GSM_WARPS
 #define GSM_WARPS 4
+#endif
+#define GSM_THREADS (GSM_WARPS * 32)
+#define GSM_PASS_ROWS (GSM_THREADS / 64)     // stage rows one pass of all threads copies
+#define GSM_RUNS (GSM_STAGE_K / GSM_WARPS / 32)   // runs of 32 k-values per warp and stage
 #define GSM_STAGE_K 512                    // k-values per stage
 #define GSM_STAGES 4
 #define GSM_ROW_BYTES (GSM_STAGE_K * 2 + 64)   // row stride = 64 mod 128 bytes: 16-byte reads of 8 rows x 4 pieces hit every bank once
@@ -35,56 +47,116 @@ __device__ __forceinline__ void gsm_mma(float (&c)[4], unsigned a0, unsigned a1,
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ void gsm_cp_async16(void* smem, const void* gmem, bool valid) {
-    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
-    const int bytes = valid ? 16 : 0;       // 0: zero-fill
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
+// Queueing a stage.  64 pieces of 16 bytes a row, GSM_PASS_ROWS rows per pass of all threads: thread
+// `tid` always copies piece `tid & 63` of rows `GSM_PASS_ROWS * i + (tid >> 6)`, so a warp request covers 512 contiguous bytes of
+// one row, and everything but the k-offset is the same for every stage.
+struct GsmCopy {
+    const bf16* W; const bf16* x;
+    const bf16* w;      // W + (n0 + (tid >> 6)) * K + (tid & 63) * 8   (short path)
+    const bf16* xs;     // x + (tid >> 6) * K + (tid & 63) * 8
+    unsigned ring;      // shared address of the ring
+    unsigned dst;       // ring + (tid >> 6) * ROW_BYTES + (tid & 63) * 16
+    int n0, N, M, K, tid;
+    bool short_path;    // all 16 weight rows of the block exist
+};
+
+__device__ __forceinline__ void gsm_cp16(unsigned dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
 }
 
-// Queue one stage: weight rows n0..n0+15 and, when XROWS > 0, the activations of tokens 0..XROWS-1
-// (stage rows 16..), k-values k0..k0+511.  128 threads, 64 pieces of 16 bytes a row: a warp request
-// covers 512 contiguous bytes of one row.
-// FIRST_ROW..LAST_ROW select weight rows (0..15), activation rows (16..) or both.
+__device__ __forceinline__ void gsm_cp16_zfill(unsigned dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;       // 0: zero-fill
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+
+// Rows FIRST..LAST-1 of a stage (0..15 weights, 16.. activations of tokens 0..), k-values k0..k0+511.
+// A stage wholly inside K of a block with all its weight rows takes the short path: straight-line
+// copies from one base pointer plus multiples of the row stride.  Everything else (the last, partial
+// stage, whose tail must be zero because it enters the sums; the last block of an N that is no
+// multiple of 16) takes the general path, which zero-fills what does not exist.
 template <int FIRST_ROW, int LAST_ROW>
-__device__ __forceinline__ void gsm_issue_stage(const bf16* __restrict__ W, const bf16* __restrict__ x,
-                                                unsigned char* stage, int n0, int N, int M, int K, int k0, int tid) {
+__device__ __forceinline__ void gsm_issue_rows(const GsmCopy& c, unsigned stage_offset, int k0) {
+    if (c.short_path && k0 + GSM_STAGE_K <= c.K) {
+        const bf16* w = c.w + k0;
+        const bf16* xs = c.xs + k0;
+        const unsigned dst = c.dst + stage_offset;
+        const int half = c.tid >> 6;
 #pragma unroll
-    for (int i = FIRST_ROW * 64 / 128; i < LAST_ROW * 64 / 128; ++i) {
-        const int idx = i * 128 + tid;
+        for (int row2 = FIRST_ROW; row2 < LAST_ROW; row2 += GSM_PASS_ROWS) {
+            if (row2 < GSM_ROWS) {
+                gsm_cp16(dst + row2 * GSM_ROW_BYTES, w + (size_t)row2 * c.K);
+            } else if (row2 - GSM_ROWS + half < c.M) {    // a token past M feeds only its own, unwritten column
+                gsm_cp16(dst + row2 * GSM_ROW_BYTES, xs + (size_t)(row2 - GSM_ROWS) * c.K);
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int i = FIRST_ROW * 64 / GSM_THREADS; i < LAST_ROW * 64 / GSM_THREADS; ++i) {
+        const int idx = i * GSM_THREADS + c.tid;
         const int row = idx >> 6, piece = idx & 63;
         const int k = k0 + piece * 8;
         const bool is_w = row < GSM_ROWS;
-        const int src_row = is_w ? n0 + row : row - GSM_ROWS;
-        const bool valid = (k < K) && (is_w ? src_row < N : src_row < M);   // K is a multiple of 8
-        const bf16* src = (is_w ? W : x) + (size_t)(valid ? src_row : 0) * K + (valid ? k : 0);
-        gsm_cp_async16(stage + row * GSM_ROW_BYTES + piece * 16, src, valid);
+        const int src_row = is_w ? c.n0 + row : row - GSM_ROWS;
+        const bool valid = (k < c.K) && (is_w ? src_row < c.N : src_row < c.M);   // K is a multiple of 8
+        const bf16* src = (is_w ? c.W : c.x) + (size_t)(valid ? src_row : 0) * c.K + (valid ? k : 0);
+        gsm_cp16_zfill(c.ring + stage_offset + row * GSM_ROW_BYTES + piece * 16, src, valid);
     }
 }
 
-// NT: token tiles of 8.  XS = 1: activations travel through the ring with the weights.  (XS = 0 reads
+// The norm weight's k-values k0..k0+511 into a stage row of their own (64 pieces of 16 bytes).
+__device__ __forceinline__ void gsm_issue_norm_row(const bf16* __restrict__ norm_w, unsigned row_dst, int K, int k0,
+                                                   int tid) {
+    if (tid < 64) {
+        const int k = k0 + tid * 8;
+        const bool valid = k < K;
+        gsm_cp16_zfill(row_dst + tid * 16, norm_w + (valid ? k : 0), valid);
+    }
+}
+
+__device__ __forceinline__ unsigned gsm_mul2(unsigned a, unsigned b) {
+    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const unsigned*>(&r);
+}
+
+// NT: token tiles of 8.  NORM = 1: fused RMSNorm (see the top of the file).  XS = 1: activations travel through the ring with the weights.  (XS = 0 reads
 // them from global memory in the threads that need them; measured slower at every token count, because
 // those reads miss the small L1 left beside the ring and stall the warp.  Kept for comparison.)
-template <int NT, int XS>
+template <int NT, int XS, int NORM>
 __global__ void __launch_bounds__(GSM_WARPS * 32)
 gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const bf16* __restrict__ bias,
-                    const bf16* residual, void* out, int M, int N, int K, int out_f32, int silu_pairs) {
+                    const bf16* residual, void* out, const bf16* __restrict__ norm_w, float norm_eps,
+                    int M, int N, int K, int out_f32, int silu_pairs) {
     extern __shared__ __align__(128) unsigned char ring[];          // [STAGES][STAGE_BYTES]
     constexpr int XROWS = XS ? 8 * NT : 0;
-    constexpr int STAGE_BYTES = (GSM_ROWS + XROWS) * GSM_ROW_BYTES;
+    constexpr int NORM_ROW = GSM_ROWS + XROWS;                      // the stage row of the norm weight
+    constexpr int STAGE_BYTES = (GSM_ROWS + XROWS + NORM) * GSM_ROW_BYTES;
     constexpr int STAGES = (XS && NT == 2) ? 3 : GSM_STAGES;
     __shared__ float red[GSM_WARPS][GSM_ROWS][8 * NT + 1];
+    __shared__ float squares[GSM_WARPS][8 * NT];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * GSM_ROWS;
     const int stages_total = (K + GSM_STAGE_K - 1) / GSM_STAGE_K;
+    GsmCopy copy;
+    copy.W = W; copy.x = x; copy.n0 = n0; copy.N = N; copy.M = M; copy.K = K; copy.tid = tid;
+    copy.short_path = n0 + GSM_ROWS <= N;
+    copy.w = W + (size_t)(copy.short_path ? n0 + (tid >> 6) : 0) * K + (tid & 63) * 8;
+    copy.xs = x + (size_t)((tid >> 6) < M ? (tid >> 6) : 0) * K + (tid & 63) * 8;
+    copy.ring = (unsigned)__cvta_generic_to_shared(ring);
+    copy.dst = copy.ring + (tid >> 6) * GSM_ROW_BYTES + (tid & 63) * 16;
+    const unsigned ring_address = copy.ring;
 
     // Weights do not depend on the kernel before this one: their first stages are requested before the
     // wait for that kernel, the activations (its output) right after.  Groups: W0..W(S-2), X0..X(S-2),
     // then one group per later stage; "at most S-2 groups pending" still means "stage s has landed".
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < stages_total)
-            gsm_issue_stage<0, GSM_ROWS>(W, x, ring + s * STAGE_BYTES, n0, N, M, K, s * GSM_STAGE_K, tid);
+        if (s < stages_total) {
+            gsm_issue_rows<0, GSM_ROWS>(copy, s * STAGE_BYTES, s * GSM_STAGE_K);
+            if (NORM) gsm_issue_norm_row(norm_w, ring_address + s * STAGE_BYTES + NORM_ROW * GSM_ROW_BYTES, K,
+                                         s * GSM_STAGE_K, tid);
+        }
         asm volatile("cp.async.commit_group;\n" ::);
     }
     qil_wait_for_producer();
@@ -92,7 +164,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
         if (XS && s < stages_total)
-            gsm_issue_stage<GSM_ROWS, GSM_ROWS + XROWS>(W, x, ring + s * STAGE_BYTES, n0, N, M, K, s * GSM_STAGE_K, tid);
+            gsm_issue_rows<GSM_ROWS, GSM_ROWS + XROWS>(copy, s * STAGE_BYTES, s * GSM_STAGE_K);
         asm volatile("cp.async.commit_group;\n" ::);
     }
 
@@ -105,8 +177,14 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
         xp[j] = x + (size_t)(ok_x[j] ? token : 0) * K + 8 * t;
     }
     float acc[NT][4];
+    // With the norm: X X^T of the token tile on the tensor cores, of which the diagonal is each token's
+    // sum of squares (products of bfloat16 values are exact in float32, the sums are float32).
+    float gram[NORM ? NT : 1][4];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int j = 0; j < NT; ++j) {
+        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        if (NORM) gram[j][0] = gram[j][1] = gram[j][2] = gram[j][3] = 0.f;
+    }
 
     for (int s = 0; s < stages_total; ++s) {
         // stage s has landed once at most STAGES-2 newer groups are still in flight
@@ -114,17 +192,20 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
         __syncthreads();            // visible to all; everyone is also done with stage s-1's buffer
         {
             const int next = s + STAGES - 1;
-            if (next < stages_total)
-                gsm_issue_stage<0, GSM_ROWS + XROWS>(W, x, ring + (next % STAGES) * STAGE_BYTES, n0, N, M, K,
-                                                     next * GSM_STAGE_K, tid);
+            if (next < stages_total) {
+                const unsigned offset = (next % STAGES) * STAGE_BYTES;
+                gsm_issue_rows<0, GSM_ROWS + XROWS>(copy, offset, next * GSM_STAGE_K);
+                if (NORM) gsm_issue_norm_row(norm_w, ring_address + offset + NORM_ROW * GSM_ROW_BYTES, K,
+                                             next * GSM_STAGE_K, tid);
+            }
             asm volatile("cp.async.commit_group;\n" ::);
         }
         const unsigned char* stage = ring + (s % STAGES) * STAGE_BYTES;
-        // this warp's quarter of the stage: 128 k-values = 4 runs of 32
+        // this warp's share of the stage: GSM_RUNS runs of 32 k-values
         const int kw = warp * (GSM_STAGE_K / GSM_WARPS);
-        uint4 vx[4][NT];
+        uint4 vx[GSM_RUNS][NT];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < GSM_RUNS; ++r) {
             const int k = s * GSM_STAGE_K + kw + r * 32;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
@@ -136,9 +217,20 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
                     if (ok_x[j] && k + 8 * t < K) vx[r][j] = *reinterpret_cast<const uint4*>(xp[j] + k);
                 }
             }
+            if (NORM) {
+                const uint4 vn = *reinterpret_cast<const uint4*>(stage + NORM_ROW * GSM_ROW_BYTES + (kw + r * 32 + 8 * t) * 2);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    // the activations as both operands: rows = tokens 8j..8j+7 (rows 8..15 of the tile are zero)
+                    gsm_mma(gram[j], vx[r][j].x, 0u, vx[r][j].y, 0u, vx[r][j].x, vx[r][j].y);
+                    gsm_mma(gram[j], vx[r][j].z, 0u, vx[r][j].w, 0u, vx[r][j].z, vx[r][j].w);
+                    vx[r][j] = make_uint4(gsm_mul2(vx[r][j].x, vn.x), gsm_mul2(vx[r][j].y, vn.y),
+                                          gsm_mul2(vx[r][j].z, vn.z), gsm_mul2(vx[r][j].w, vn.w));
+                }
+            }
         }
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < GSM_RUNS; ++r) {
             const int byte = (kw + r * 32 + 8 * t) * 2;
             const uint4 va = *reinterpret_cast<const uint4*>(stage + g * GSM_ROW_BYTES + byte);
             const uint4 vb = *reinterpret_cast<const uint4*>(stage + (g + 8) * GSM_ROW_BYTES + byte);
@@ -157,8 +249,18 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
         red[warp][g][8 * j + 2 * t + 1] = acc[j][1];
         red[warp][g + 8][8 * j + 2 * t] = acc[j][2];
         red[warp][g + 8][8 * j + 2 * t + 1] = acc[j][3];
+        // gram[j][0..1] are entries (g, 2t) and (g, 2t + 1): the diagonal one belongs to thread t == g / 2
+        if (NORM && t == (g >> 1)) squares[warp][8 * j + g] = (g & 1) ? gram[j][1] : gram[j][0];
     }
     __syncthreads();
+    // 1 / rms of a token's activations, the warps' partial sums added in warp order
+    auto inverse_rms = [&](int token) {
+        if (!NORM) return 1.f;
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < GSM_WARPS; ++w) total += squares[w][token];
+        return rsqrtf(total / (float)K + norm_eps);
+    };
     if (silu_pairs) {
         // rows 0..7 of the block are gate features, rows 8..15 the matching up features
         const int out_width = N / 2;
@@ -169,8 +271,9 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
             float gate = 0.f, up = 0.f;
 #pragma unroll
             for (int w = 0; w < GSM_WARPS; ++w) { gate += red[w][r][token]; up += red[w][r + 8][token]; }
-            gate = round_to<bf16>(gate);
-            up = round_to<bf16>(up);
+            const float scale = inverse_rms(token);
+            gate = round_to<bf16>(gate * scale);
+            up = round_to<bf16>(up * scale);
             const float act = round_to<bf16>(__fdividef(gate, 1.0f + __expf(-gate)));   // as the stand-alone bfloat16 kernel
             reinterpret_cast<bf16*>(out)[(size_t)token * out_width + col] = __float2bfloat16_rn(act * up);
         }
@@ -183,6 +286,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < GSM_WARPS; ++w) v += red[w][r][token];
+        v *= inverse_rms(token);
         if (bias != nullptr) v += __bfloat162float(bias[n]);
         if (residual != nullptr) v = __bfloat162float(residual[(size_t)token * N + n]) + v;
         if (out_f32) reinterpret_cast<float*>(out)[(size_t)token * N + n] = v;
@@ -192,31 +296,40 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
 
 extern "C" int qil_gemm_small_m_max_rows() { return 16; }
 
+// norm_w: null, or the K weights of the RMSNorm to apply to x first (with norm_eps).
 extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, const void* residual, void* out,
-                                int M, int N, int K, int out_f32, int silu_pairs, cudaStream_t stream) {
+                                const void* norm_w, float norm_eps, int M, int N, int K, int out_f32, int silu_pairs,
+                                cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16) QIL_REFUSE("gemm_small_m: %d rows; this kernel takes at most 16", M);
     if (K <= 0 || K % 8) QIL_REFUSE("gemm_small_m: K %d must be a positive multiple of 8", K);
-    if (((uintptr_t)x | (uintptr_t)W) & 15) QIL_REFUSE("gemm_small_m: x and W must be 16-byte aligned");
+    if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)norm_w) & 15)
+        QIL_REFUSE("gemm_small_m: x, W and the norm weight must be 16-byte aligned");
     if (silu_pairs && (N % 16 || bias != nullptr || residual != nullptr || out_f32))
         QIL_REFUSE("gemm_small_m: silu_pairs needs N %% 16 == 0 and no bias, residual or float32 output");
     const int blocks = (N + GSM_ROWS - 1) / GSM_ROWS;
-    const int smem_staged1 = GSM_STAGES * (GSM_ROWS + 8) * GSM_ROW_BYTES;
-    const int smem_staged2 = 3 * (GSM_ROWS + 16) * GSM_ROW_BYTES;
+    const int smem1 = GSM_STAGES * (GSM_ROWS + 8) * GSM_ROW_BYTES, smem1n = GSM_STAGES * (GSM_ROWS + 8 + 1) * GSM_ROW_BYTES;
+    const int smem2 = 3 * (GSM_ROWS + 16) * GSM_ROW_BYTES, smem2n = 3 * (GSM_ROWS + 16 + 1) * GSM_ROW_BYTES;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e1 = cudaSuccess;
-        cudaError_t e2 = cudaFuncSetAttribute(gemm_small_m_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_staged1);
-        cudaError_t e3 = cudaFuncSetAttribute(gemm_small_m_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_staged2);
-        if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess)
-            QIL_REFUSE("gemm_small_m: cannot reserve %d bytes of shared memory", smem_staged1);
+        cudaError_t e[4] = {
+            cudaFuncSetAttribute(gemm_small_m_kernel<1, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1),
+            cudaFuncSetAttribute(gemm_small_m_kernel<2, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2),
+            cudaFuncSetAttribute(gemm_small_m_kernel<1, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1n),
+            cudaFuncSetAttribute(gemm_small_m_kernel<2, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2n)};
+        for (int i = 0; i < 4; ++i)
+            if (e[i] != cudaSuccess) QIL_REFUSE("gemm_small_m: cannot reserve %d bytes of shared memory", smem1n);
         configured = true;
     }
-    if (M <= 8)
-        qil_launch_chained(gemm_small_m_kernel<1, 1>, dim3(blocks), dim3(GSM_WARPS * 32), smem_staged1, stream,
-            (const bf16*)x, (const bf16*)W, (const bf16*)bias, (const bf16*)residual, out, M, N, K, out_f32, silu_pairs);
-    else
-        qil_launch_chained(gemm_small_m_kernel<2, 1>, dim3(blocks), dim3(GSM_WARPS * 32), smem_staged2, stream,
-            (const bf16*)x, (const bf16*)W, (const bf16*)bias, (const bf16*)residual, out, M, N, K, out_f32, silu_pairs);
+#define GSM_LAUNCH(NT, NORM, SMEM)                                                                                  \
+    qil_launch_chained(gemm_small_m_kernel<NT, 1, NORM>, dim3(blocks), dim3(GSM_WARPS * 32), SMEM, stream,           \
+                       (const bf16*)x, (const bf16*)W, (const bf16*)bias, (const bf16*)residual, out,                \
+                       (const bf16*)norm_w, norm_eps, M, N, K, out_f32, silu_pairs)
+    if (norm_w == nullptr) {
+        if (M <= 8) GSM_LAUNCH(1, 0, smem1); else GSM_LAUNCH(2, 0, smem2);
+    } else {
+        if (M <= 8) GSM_LAUNCH(1, 1, smem1n); else GSM_LAUNCH(2, 1, smem2n);
+    }
+#undef GSM_LAUNCH
     QIL_CHECK_LAUNCH();
 }

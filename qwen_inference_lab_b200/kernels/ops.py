@@ -130,12 +130,14 @@ def small_m_ok(a, weight) -> bool:
             and weight.shape[1] % 8 == 0 and a.is_contiguous())
 
 
-def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=False, silu_pairs=False):
+def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=False, silu_pairs=False,
+                 norm_weight=None, norm_eps=0.0):
     """out = a @ weight.T (+ bias) (+ residual) for a decode step's few rows, streaming the weight once.
 
     a bfloat16 [M <= 16, K]; weight bfloat16 [N, K].  ``out_float32`` returns float32 (the LM head).
     ``silu_pairs``: weight rows are groups of [8 gate, 8 up]; returns silu(gate) * up, bfloat16 [M, N/2].
-    ``residual`` may be ``out`` itself.
+    ``residual`` may be ``out`` itself.  With ``norm_weight`` (bfloat16 [K]) the kernel first applies
+    RMSNorm(a; norm_weight, norm_eps): the product of the normed rows, with no pass of its own over them.
     """
     _need(a, "a", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
     m, k = a.shape
@@ -155,8 +157,13 @@ def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=Fals
     _need(out, "out", out_dtype, 2)
     if out.shape != out_shape:
         raise KernelError("gemm_small_m: out has the wrong shape")
+    if norm_weight is not None:
+        _need(norm_weight, "norm_weight", torch.bfloat16, 1)
+        if norm_weight.shape[0] != k:
+            raise KernelError("gemm_small_m: the norm weight must have one value per input feature")
     lib = core()
-    _check(lib, lib.qil_gemm_small_m(_p(a), _p(weight), _p(bias), _p(residual), _p(out), c_int(m), c_int(n), c_int(k),
+    _check(lib, lib.qil_gemm_small_m(_p(a), _p(weight), _p(bias), _p(residual), _p(out), _p(norm_weight),
+                                     c_float(float(norm_eps)), c_int(m), c_int(n), c_int(k),
                                      c_int(1 if out_float32 else 0), c_int(1 if silu_pairs else 0), _stream()),
            "gemm_small_m")
     return out

@@ -71,11 +71,14 @@ class GroupedQueryAttention(Mixer):
             return None
         return KVCacheSpec(self.n_kv_heads, self.head_dim, self.window)
 
-    def forward(self, ctx, x, cache, residual=None):
-        """x [N, hidden] -> [N, hidden] (+ residual).  ``cache`` is a KVCacheView."""
+    takes_norm = True
+
+    def forward(self, ctx, x, cache, residual=None, norm=None):
+        """x [N, hidden] -> [N, hidden] (+ residual).  ``cache`` is a KVCacheView.  With ``norm`` x is
+        the block's un-normed input and the first projection applies the norm."""
         n = x.shape[0]
         n_kv = 0 if self.reads_shared_cache else self.n_kv_heads
-        qkv = self.qkv.forward(ctx, x)
+        qkv = self.qkv.forward(ctx, x, norm=norm)
         q = ctx.empty((n, self.n_q_heads * self.head_dim))
         table = self.position.table if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0

@@ -14,8 +14,11 @@ Interfaces
 ``PositionEncoding``  ``table`` (float32 ``[positions, rotary_dim]``: cosines then
                 sines) and ``rotary_dim``; mixers hand the table to their kernels.
 ``Mixer``       ``cache_spec()`` (what it keeps per request: paged keys/values, a
-                fixed-size state, or nothing) and ``forward(ctx, x, cache) -> y``.
+                fixed-size state, or nothing) and ``forward(ctx, x, cache, residual=None) -> y``.
 ``FeedForward`` ``forward(ctx, x, residual=None) -> y``.
+                A mixer or feed-forward with ``takes_norm = True`` is handed the block's
+                un-normed input and the norm (``norm=``) and applies it itself, so that it can
+                fuse the norm into its first product; the others get normed input.
 ``Block``       ``forward(ctx, x, cache) -> x`` (arrangement of the above).
 """
 from __future__ import annotations
@@ -100,6 +103,11 @@ class Part:
 class Norm(Part):
     def forward(self, ctx, x, rows=None):
         raise NotImplementedError
+
+    def as_rms(self):
+        """(weight tensor, eps) if this norm is a plain root-mean-square norm that a product kernel
+        may apply itself, else None."""
+        return None
 
 
 class PositionEncoding(Part):

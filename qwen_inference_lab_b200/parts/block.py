@@ -24,5 +24,10 @@ class PreNormBlock(Part):
 
     def forward(self, ctx, x, cache):
         """x [N, hidden] is the residual stream; returned updated (possibly in place)."""
-        x = self.mixer.forward(ctx, self.mixer_norm.forward(ctx, x), cache, residual=x)
+        if getattr(self.mixer, "takes_norm", False):
+            x = self.mixer.forward(ctx, x, cache, residual=x, norm=self.mixer_norm)
+        else:
+            x = self.mixer.forward(ctx, self.mixer_norm.forward(ctx, x), cache, residual=x)
+        if getattr(self.feed_forward, "takes_norm", False):
+            return self.feed_forward.forward(ctx, x, residual=x, norm=self.ff_norm)
         return self.feed_forward.forward(ctx, self.ff_norm.forward(ctx, x), residual=x)

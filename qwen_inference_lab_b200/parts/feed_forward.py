@@ -40,7 +40,17 @@ class GatedMLP(FeedForward):
                 2 * inner, self.hidden_size).contiguous()
             self.pairs8 = True
 
-    def forward(self, ctx, x, residual=None):
+    takes_norm = True
+
+    def forward(self, ctx, x, residual=None, norm=None):
+        """With ``norm`` x is the block's un-normed input; a decode step's few rows get the norm inside
+        the gate/up kernel, longer steps a norm kernel of their own."""
+        rms = norm.as_rms() if norm is not None else None
+        if self.pairs8 and ops.small_m_ok(x, self.gate_up._w) and rms is not None and rms[0].dtype == torch.bfloat16:
+            hidden = ops.gemm_small_m(x, self.gate_up._w, silu_pairs=True, norm_weight=rms[0], norm_eps=rms[1])
+            return self.down.forward(ctx, hidden, residual=residual)
+        if norm is not None:
+            x = norm.forward(ctx, x)
         if self.pairs8 and ops.small_m_ok(x, self.gate_up._w):
             hidden = ops.gemm_small_m(x, self.gate_up._w, silu_pairs=True)
         elif self.pairs8 and gemm_tc.usable(x, self.gate_up._w):

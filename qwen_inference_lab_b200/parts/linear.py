@@ -54,12 +54,23 @@ class Linear(Part):
     def _bias(self):
         return self.bias.data if self.bias is not None else None
 
-    def forward(self, ctx, x, residual=None, out=None, out_float32=False):
-        """``x`` [N, in] -> [N, out]; adds ``residual`` [N, out] when given (may be ``out``)."""
+    def forward(self, ctx, x, residual=None, out=None, out_float32=False, norm=None):
+        """``x`` [N, in] -> [N, out]; adds ``residual`` [N, out] when given (may be ``out``).
+
+        With ``norm`` (a Norm part) the product is of ``norm(x)``: fused into the kernel where it can be.
+        """
         weight, bias = self._weight(), self._bias()
         if ops.small_m_ok(x, weight):
             # a decode step's few rows: the engine's weight-streaming kernel
+            rms = norm.as_rms() if norm is not None else None
+            if rms is not None and rms[0].dtype == torch.bfloat16:
+                return ops.gemm_small_m(x, weight, bias=bias, residual=residual, out=out, out_float32=out_float32,
+                                        norm_weight=rms[0], norm_eps=rms[1])
+            if norm is not None:
+                x = norm.forward(ctx, x)
             return ops.gemm_small_m(x, weight, bias=bias, residual=residual, out=out, out_float32=out_float32)
+        if norm is not None:
+            x = norm.forward(ctx, x)
         if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
             if out_float32:
                 result = _library_mm_f32_out(x, weight)

@@ -23,3 +23,6 @@ class RMSNorm(Norm):
     def forward(self, ctx, x, rows=None):
         """Norm of every row of ``x`` [N, width], or of ``x[rows]`` when ``rows`` (int32) is given."""
         return ops.rmsnorm(x, self.weight.data, self.eps, rows=rows)
+
+    def as_rms(self):
+        return self.weight.data, self.eps

@@ -344,6 +344,40 @@ def test_gemm_small_m(m, n, k):
     assert torch.equal(alone.cpu()[0], exact.cpu()[-1])
 
 
+@pytest.mark.parametrize("m,n,k,eps", [(1, 16, 8, 1e-6), (3, 200, 96, 1e-5), (8, 136, 520, 1e-6), (9, 64, 4096, 3e-6),
+                                       (16, 1000, 1032, 1e-6)])
+def test_gemm_small_m_with_the_norm_inside(m, n, k, eps):
+    """RMSNorm fused into the product: rows of very different size (the norm must bring each to its
+    own scale), a norm weight far from one, and the same epilogues."""
+    torch.manual_seed(14)
+    a = (torch.randn(m, k) * torch.logspace(-2, 2, m).unsqueeze(1)).to(torch.bfloat16)
+    norm_w = (1 + torch.randn(k) * 0.3).to(torch.bfloat16)
+    w = (torch.randn(n, k) * 0.1).to(torch.bfloat16)
+    bias = (torch.randn(n) * 0.1).to(torch.bfloat16)
+    residual = torch.randn(m, n).to(torch.bfloat16)
+    normed = a.double() * torch.rsqrt(a.double().pow(2).mean(-1, keepdim=True) + eps) * norm_w.double()
+    product = normed @ w.double().t()
+    run = lambda **kw: ops().gemm_small_m(a.cuda(), w.cuda(), norm_weight=norm_w.cuda(), norm_eps=eps, **kw)
+    close(run(), product.float(), torch.bfloat16, scale=4)
+    close(run(bias=bias.cuda(), residual=residual.cuda()), (product + bias.double() + residual.double()).float(),
+          torch.bfloat16, scale=4)
+    exact = run(out_float32=True)
+    # one bfloat16 rounding of x * w_norm is all that separates this from the float64 product
+    torch.testing.assert_close(exact.cpu(), product.float(), atol=0.03 * float(product.abs().max()) / 4, rtol=0.02)
+    # against the two-kernel form (norm kernel, then the product): the same up to the norm's two roundings
+    separate = ops().gemm_small_m(ops().rmsnorm(a.cuda(), norm_w.cuda(), eps), w.cuda(), out_float32=True)
+    assert (exact - separate).abs().max() <= 0.03 * float(product.abs().max())
+    assert (exact.cpu() - product.float()).abs().mean() <= 1.2 * (separate.cpu() - product.float()).abs().mean()
+    alone = ops().gemm_small_m(a[-1:].cuda().contiguous(), w.cuda(), norm_weight=norm_w.cuda(), norm_eps=eps,
+                               out_float32=True)
+    assert torch.equal(alone.cpu()[0], exact.cpu()[-1])
+    if n % 16 == 0:     # the gate/up epilogue scales both halves before the activation
+        gate_up = run(silu_pairs=True)
+        half = product.float().view(m, n // 16, 2, 8)
+        expected = torch.nn.functional.silu(half[:, :, 0]) * half[:, :, 1]
+        close(gate_up, expected.reshape(m, n // 2), torch.bfloat16, scale=max(2.0, float(expected.abs().max()) / 2))
+
+
 @pytest.mark.parametrize("m,inner,k", [(1, 8, 16), (5, 200, 96), (16, 1024, 256)])
 def test_gemm_small_m_with_gate_epilogue_and_paired_silu(m, inner, k):
     torch.manual_seed(10)
