@@ -26,6 +26,7 @@
 // error word.  No multicast loads are used.
 #include "common.cuh"
 #include <cuda.h>
+#include <stdlib.h>
 
 QIL_ERROR_STORAGE
 
@@ -113,6 +114,58 @@ __device__ __forceinline__ void tmem_load_32(unsigned taddr, float (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// One warp's quarter (32 rows) of a finished 128 x 256 accumulator: tcgen05.ld 32 columns at a time,
+// epilogue, bfloat16 stores.  m is this lane's output row, n0 the tile's first output column.
+__device__ __forceinline__ void tc_store_accumulator(unsigned taddr, int m, int n0, int M, int N, int silu_pairs,
+                                                     const bf16* __restrict__ bias, const bf16* residual, bf16* out) {
+#pragma unroll 1
+    for (int c = 0; c < TC_BN / 32; ++c) {
+        float v[32];
+        __syncwarp();                              // the load below is a warp-wide instruction
+        tmem_load_32(taddr + c * 32, v);
+        const int n = n0 + c * 32;
+        if (m >= M || n >= N) {
+            // nothing to store for this lane
+        } else if (silu_pairs) {
+            // columns come as [8 gate, 8 up] groups: 32 columns give 16 outputs
+            const int out_width = N / 2;
+            bf16* dst = out + (size_t)m * out_width + n / 2;
+#pragma unroll
+            for (int grp = 0; grp < 2; ++grp) {
+                uint4 packed;
+                bf16* o = reinterpret_cast<bf16*>(&packed);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float gate = round_to<bf16>(v[grp * 16 + i]);
+                    const float up = round_to<bf16>(v[grp * 16 + 8 + i]);
+                    const float act = round_to<bf16>(__fdividef(gate, 1.0f + __expf(-gate)));
+                    o[i] = __float2bfloat16_rn(act * up);
+                }
+                if (n + grp * 16 < N) *reinterpret_cast<uint4*>(dst + grp * 8) = packed;
+            }
+        } else {
+            bf16* dst = out + (size_t)m * N + n;
+            const bf16* res = residual ? residual + (size_t)m * N + n : nullptr;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (n + q * 8 >= N) break;
+                uint4 packed, rv = make_uint4(0u, 0u, 0u, 0u);
+                if (res) rv = *reinterpret_cast<const uint4*>(res + q * 8);
+                const bf16* r8 = reinterpret_cast<const bf16*>(&rv);
+                bf16* o = reinterpret_cast<bf16*>(&packed);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float x = v[q * 8 + i];
+                    if (bias) x += __bfloat162float(bias[n + q * 8 + i]);
+                    if (res) x = __bfloat162float(r8[i]) + x;
+                    o[i] = __float2bfloat16_rn(x);
+                }
+                *reinterpret_cast<uint4*>(dst + q * 8) = packed;
+            }
+        }
+    }
 }
 
 struct TcShared {
@@ -217,52 +270,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const int m = m0 + quarter * 32 + lane;
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)acc * TC_BN;
-#pragma unroll 1
-            for (int c = 0; c < TC_BN / 32; ++c) {
-                float v[32];
-                __syncwarp();                              // the load below is a warp-wide instruction
-                tmem_load_32(taddr + c * 32, v);
-                const int n = n0 + c * 32;
-                if (m >= M || n >= N) {
-                    // nothing to store for this lane
-                } else if (silu_pairs) {
-                    // columns come as [8 gate, 8 up] groups: 32 columns give 16 outputs
-                    const int out_width = N / 2;
-                    bf16* dst = out + (size_t)m * out_width + n / 2;
-#pragma unroll
-                    for (int grp = 0; grp < 2; ++grp) {
-                        uint4 packed;
-                        bf16* o = reinterpret_cast<bf16*>(&packed);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float gate = round_to<bf16>(v[grp * 16 + i]);
-                            const float up = round_to<bf16>(v[grp * 16 + 8 + i]);
-                            const float act = round_to<bf16>(__fdividef(gate, 1.0f + __expf(-gate)));
-                            o[i] = __float2bfloat16_rn(act * up);
-                        }
-                        if (n + grp * 16 < N) *reinterpret_cast<uint4*>(dst + grp * 8) = packed;
-                    }
-                } else {
-                    bf16* dst = out + (size_t)m * N + n;
-                    const bf16* res = residual ? residual + (size_t)m * N + n : nullptr;
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        if (n + q * 8 >= N) break;
-                        uint4 packed, rv = make_uint4(0u, 0u, 0u, 0u);
-                        if (res) rv = *reinterpret_cast<const uint4*>(res + q * 8);
-                        const bf16* r8 = reinterpret_cast<const bf16*>(&rv);
-                        bf16* o = reinterpret_cast<bf16*>(&packed);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            float x = v[q * 8 + i];
-                            if (bias) x += __bfloat162float(bias[n + q * 8 + i]);
-                            if (res) x = __bfloat162float(r8[i]) + x;
-                            o[i] = __float2bfloat16_rn(x);
-                        }
-                        *reinterpret_cast<uint4*>(dst + q * 8) = packed;
-                    }
-                }
-            }
+            tc_store_accumulator(taddr, m, n0, M, N, silu_pairs, bias, residual, out);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
@@ -275,6 +283,188 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ two SMs on one tile
+// The same product with pairs of blocks (a cluster of two, on neighbouring SMs) working on one
+// 256 x 256 output tile with tcgen05.mma.cta_group::2.  Each block of a pair loads its own 128 rows of A
+// and its own half (128 output features) of the W tile; one thread of the pair's first block issues the
+// MMAs, which read A and W from both blocks' shared memory and write each block's 128 x 256 half of the
+// accumulator into that block's tensor memory.  Against the one-block kernel every MMA reads half as
+// many bytes of shared memory per block (8 KB instead of 12 KB per 128 x 256 x 16 step), which is what
+// keeps the tensor pipe fed, and a stage is 32 KB instead of 48 KB, so six stages fit instead of four.
+//
+// Barriers.  full[s] lives in the first block: its producer arms it with the bytes of both blocks and
+// the second block's copies complete on it too (the barrier operand of a cta_group::2 copy may be the
+// peer's).  empty[s] and acc_full[a] exist in both blocks and are signalled by one tcgen05.commit with a
+// multicast mask of both.  acc_empty[a] lives in the first block and collects the arrivals of the eight
+// epilogue warps of the pair, the second block's through shared::cluster addresses.  Every wait is
+// local to the waiting block and bounded as in the kernel above; the pair meets at a cluster barrier
+// before either block frees its tensor memory and leaves.  None of the loads is a multicast load.
+#define T2_STAGES 6
+#define T2_A_BYTES (128 * TC_BK * 2)
+#define T2_B_BYTES (128 * TC_BK * 2)
+#define T2_STAGE_BYTES (T2_A_BYTES + T2_B_BYTES)
+
+struct Tc2Shared {
+    unsigned long long full[T2_STAGES];
+    unsigned long long empty[T2_STAGES];
+    unsigned long long acc_full[2];
+    unsigned long long acc_empty[2];
+    unsigned tmem_base;
+    unsigned pad;
+};
+
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// The shared::cluster address of the same shared-memory offset in block `rank` of the cluster.
+__device__ __forceinline__ unsigned map_to_rank(unsigned shared_addr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(shared_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+// A tile copy of a block of a pair; `bar_cluster` may be a barrier of the pair's other block.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem, const CUtensorMap* map, unsigned bar_cluster, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(smem_u32(smem)), "l"((unsigned long long)map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b,
+                                               unsigned idesc, unsigned accumulate) {
+    const unsigned zero = 0u;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
+}
+// Arrives, once the pair's MMAs so far are done, on the barrier at this offset in both blocks.
+__device__ __forceinline__ void umma_commit_pair(unsigned long long* bar) {
+    const unsigned short both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(smem_u32(bar)), "h"(both) : "memory");
+}
+// bfloat16 x bfloat16 -> float32, both operands K-major, M = 256 over the pair, N = 256.
+__device__ __forceinline__ unsigned umma_idesc_pair() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(256 >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const bf16* __restrict__ bias, const bf16* residual, bf16* out,
+                    int M, int N, int K, int silu_pairs, int* error_word) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    Tc2Shared* sh = reinterpret_cast<Tc2Shared*>(tiles + T2_STAGES * T2_STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int tiles_m = (M + 255) / 256, tiles_n = (N + TC_BN - 1) / TC_BN;
+    const int n_tiles = tiles_m * tiles_n;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T2_STAGES; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&sh->acc_full[a], 1); mbar_init(&sh->acc_empty[a], 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {     // the same warp of both blocks, the same address: the pair's allocation
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&sh->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the other block's barriers are initialised before anything arrives on them
+    tc_fence_after();
+    const unsigned tmem_base = sh->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_w) : "memory");
+            int stage = 0;
+            unsigned phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+                const int m0 = (tile % tiles_m) * 256 + (int)rank * 128, n0 = (tile / tiles_m) * TC_BN + (int)rank * 128;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&sh->empty[stage], phase ^ 1)) { atomicExch(error_word, 1); ok = false; break; }
+                    if (rank == 0) mbar_arrive_expect_tx(&sh->full[stage], 2 * T2_STAGE_BYTES);
+                    const unsigned full_of_first = map_to_rank(smem_u32(&sh->full[stage]), 0);
+                    unsigned char* a_dst = tiles + stage * T2_STAGE_BYTES;
+                    tma_load_2d_pair(a_dst, &map_a, full_of_first, kb * TC_BK, m0);
+                    tma_load_2d_pair(a_dst + T2_A_BYTES, &map_w, full_of_first, kb * TC_BK, n0);
+                    if (++stage == T2_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            for (int i = 0; i < T2_STAGES; ++i) {      // this block's copies in flight land before it leaves
+                if (!mbar_wait(&sh->empty[stage], phase ^ 1)) { atomicExch(error_word, 2); break; }
+                if (++stage == T2_STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const unsigned idesc = umma_idesc_pair();
+            int stage = 0, acc = 0;
+            unsigned phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+                if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1)) { atomicExch(error_word, 3); ok = false; break; }
+                tc_fence_after();
+                const unsigned tmem_d = tmem_base + (unsigned)acc * TC_BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&sh->full[stage], phase)) { atomicExch(error_word, 4); ok = false; break; }
+                    tc_fence_after();
+                    const unsigned a_addr = smem_u32(tiles + stage * T2_STAGE_BYTES);
+                    const unsigned b_addr = a_addr + T2_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_bf16_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc,
+                                       (kb | k) ? 1u : 0u);
+                    umma_commit_pair(&sh->empty[stage]);
+                    if (++stage == T2_STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(&sh->acc_full[acc]);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int acc = 0;
+        unsigned acc_phase = 0;
+        bool ok = true;
+        for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+            const int m0 = (tile % tiles_m) * 256 + (int)rank * 128, n0 = (tile / tiles_m) * TC_BN;
+            if (!mbar_wait(&sh->acc_full[acc], acc_phase)) { if (lane == 0) atomicExch(error_word, 5); ok = false; break; }
+            tc_fence_after();
+            const int m = m0 + quarter * 32 + lane;
+            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)acc * TC_BN;
+            tc_store_accumulator(taddr, m, n0, M, N, silu_pairs, bias, residual, out);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&sh->acc_empty[acc]), 0));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // neither block leaves while the other may still read its tiles or signal it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -333,6 +523,34 @@ extern "C" int qil_gemm_tc(const void* a, const void* w, const void* bias, const
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) QIL_REFUSE("gemm_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
+    }
+    static int pair_env = -1;
+    if (pair_env < 0) {
+        const char* e = getenv("QIL_GEMM_TC_PAIRS");
+        pair_env = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    if (M >= 256 && pair_env == 1) {
+        // two SMs per 256 x 256 tile; the W map's box is the 128 output features one block loads
+        if (make_map(&map_w, w, N, K, 128)) return -1;
+        const int smem_pair = T2_STAGES * T2_STAGE_BYTES + (int)sizeof(Tc2Shared) + 1024;
+        static int pairs_resident = 0;
+        if (pairs_resident == 0) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair);
+            if (e != cudaSuccess) QIL_REFUSE("gemm_tc: cannot reserve %d bytes of shared memory: %s", smem_pair, cudaGetErrorString(e));
+            cudaLaunchConfig_t config = {};
+            config.gridDim = dim3(sm_count & ~1);
+            config.blockDim = dim3(192);
+            config.dynamicSmemBytes = smem_pair;
+            int clusters = 0;
+            e = cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_pair_kernel, &config);
+            if (e != cudaSuccess || clusters <= 0) { (void)cudaGetLastError(); clusters = sm_count / 2; }
+            pairs_resident = clusters < sm_count / 2 ? clusters : sm_count / 2;
+        }
+        const int pair_tiles = ((M + 255) / 256) * ((N + TC_BN - 1) / TC_BN);
+        const int pairs = pair_tiles < pairs_resident ? pair_tiles : pairs_resident;
+        gemm_tc_pair_kernel<<<2 * pairs, 192, smem_pair, stream>>>(map_a, map_w, (const bf16*)bias, (const bf16*)residual,
+                                                                   (bf16*)out, M, N, K, silu_pairs, error_word);
+        QIL_CHECK_LAUNCH();
     }
     const int n_tiles = ((M + TC_BM - 1) / TC_BM) * ((N + TC_BN - 1) / TC_BN);
     const int blocks = n_tiles < sm_count ? n_tiles : sm_count;
