@@ -318,8 +318,10 @@ def run_ours(args):
         print(f"decode batch {batch} context {args.context} layers {cfg['num_hidden_layers']}: {part['ms_per_step']:.3f} ms/step")
         return
     if args.only == "prefill":
-        ms = bench.prefill(PREFILL_TOKENS, reps=args.steps if args.steps != 32 else 2, warmup=3)
-        print(f"prefill {PREFILL_TOKENS} tokens layers {cfg['num_hidden_layers']}: {ms:.3f} ms (all: {bench.last_prefill_times})")
+        ms = bench.prefill(args.prefill_tokens, reps=args.steps if args.steps != 32 else 2, warmup=3)
+        frac = prefill_flops(cfg, args.prefill_tokens) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+        print(f"prefill {args.prefill_tokens} tokens layers {cfg['num_hidden_layers']}: {ms:.3f} ms "
+              f"({args.prefill_tokens / ms * 1e3:.0f} tokens/s, {frac:.3f} of the bf16 peak; all: {bench.last_prefill_times})")
         return
     main = bench.decode(batch, context, args.steps, args.warmup, sample_clocks=True)
     points = {}
@@ -449,6 +451,8 @@ def main():
     parser.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes (default: Qwen3-8B)")
     parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     parser.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per request (profiling aid)")
+    parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                        help="prompt length of --only prefill (the JSON line always uses 2048)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
