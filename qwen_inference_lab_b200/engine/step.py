@@ -55,6 +55,7 @@ class StepRunner:
         self._graphs: dict = {}
         self._graph_pool = None
         self._extras: dict = {}      # what parts keep from step to step (scratch buffers), by their own keys
+        self._single_token_template = None
         self._reserve(8 * max_step_tokens + 16 * cache.max_requests + 64)
         self.steps_run = 0
         self.kernel_launches = 0          # this engine's own kernels (library products are not counted)
@@ -92,8 +93,35 @@ class StepRunner:
             if any(type(w) is not int or not 0 <= w < len(tokens) for w in entry.want):
                 raise StepError(f"request {entry.request_id!r}: wanted places must index its tokens of this step")
 
+    def _describe_single_tokens(self, entries):
+        """The description of a step in which every request brings one token.  Consecutive decode steps
+        of the same requests differ only in the tokens and the positions: the packed vector of the last
+        such step is kept and those entries are overwritten."""
+        key = tuple((e.request_id, tuple(e.want)) for e in entries)
+        starts = np.fromiter((self.cache.written(e.request_id) for e in entries), dtype=np.int64, count=len(entries))
+        kept = self._single_token_template
+        if kept is None or kept[0] != key:
+            packed, offsets, host, n, s, _ = self._describe_general(entries)
+            self._single_token_template = kept = (key, packed, offsets, host)
+        _, packed, offsets, host = kept
+        n = len(entries)
+        begin = offsets["token_ids"][0]
+        packed[begin:begin + n] = [e.tokens[0] for e in entries]
+        for name in ("positions", "seg_pos0"):
+            begin = offsets[name][0]
+            packed[begin:begin + n] = starts
+        begin = offsets["decode_info"][0]
+        packed[begin + 1:begin + 4 * n:4] = starts
+        host = dict(host, seg_pos0=starts)
+        return packed, offsets, host, n, n, int(starts.max()) + 1
+
     def _describe(self, entries):
         """Host arrays of the batch, packed into one int32 vector with section offsets."""
+        if all(len(e.tokens) == 1 for e in entries):
+            return self._describe_single_tokens(entries)
+        return self._describe_general(entries)
+
+    def _describe_general(self, entries):
         lens = np.array([len(e.tokens) for e in entries], dtype=np.int64)
         starts = np.array([self.cache.written(e.request_id) for e in entries], dtype=np.int64)
         rows = np.array([self.cache.row(e.request_id) for e in entries], dtype=np.int64)

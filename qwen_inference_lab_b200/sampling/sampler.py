@@ -21,13 +21,26 @@ class NonFiniteLogits(RuntimeError):
 class Sampler:
     def __init__(self, device, max_rows=256):
         self.device = torch.device(device)
-        self._result = torch.zeros((2, max_rows), dtype=torch.int32, device=self.device)
-        self._host = torch.zeros((2, max_rows), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        self._views = {}
+        self._allocate(max_rows)
+
+    def _allocate(self, rows):
+        self._result = torch.zeros((2, rows), dtype=torch.int32, device=self.device)
+        self._host = torch.zeros((2, rows), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        self._host_numpy = self._host.numpy()
+        self._views.clear()
 
     def _reserve(self, rows):
         if rows > self._result.shape[1]:
-            self._result = torch.zeros((2, rows), dtype=torch.int32, device=self.device)
-            self._host = torch.zeros((2, rows), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            self._allocate(rows)
+
+    def _buffers(self, rows):
+        """(tokens, flags) on the device, the (device, host) pair of the read-back, for this row count."""
+        views = self._views.get(rows)
+        if views is None:
+            views = (self._result[0, :rows], self._result[1, :rows], self._result[:, :rows], self._host[:, :rows])
+            self._views[rows] = views
+        return views
 
     def choose(self, logits, temperatures=None, seeds=None, counters=None) -> list:
         """One token id per row of float32 ``logits`` [R, V]; waits for the result.
@@ -42,9 +55,10 @@ class Sampler:
             t = torch.tensor(list(temperatures), dtype=torch.float32).to(self.device, non_blocking=True)
             s = torch.tensor([v & 0x7FFFFFFFFFFFFFFF for v in seeds], dtype=torch.int64).to(self.device, non_blocking=True)
             c = torch.tensor(list(counters), dtype=torch.int64).to(self.device, non_blocking=True)
-        ops.sample_rows(logits, t, s, c, tokens=self._result[0, :rows], nonfinite=self._result[1, :rows])
-        self._host[:, :rows].copy_(self._result[:, :rows], non_blocking=True)
+        tokens, flags, device_pair, host_pair = self._buffers(rows)
+        ops.sample_rows(logits, t, s, c, tokens=tokens, nonfinite=flags)
+        host_pair.copy_(device_pair, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        if int(self._host[1, :rows].max()) != 0:
+        if self._host_numpy[1, :rows].any():
             raise NonFiniteLogits("model returned non-finite logits")
-        return self._host[0, :rows].tolist()
+        return self._host_numpy[0, :rows].tolist()
