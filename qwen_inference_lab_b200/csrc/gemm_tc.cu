@@ -116,6 +116,107 @@ __device__ __forceinline__ void tmem_load_32(unsigned taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The query/key/value projection can end in what otherwise is a kernel of its own: per-head RMSNorm of
+// queries and keys, the rotation of both by the token's position, queries to their buffer and keys and
+// values into the token's page of the cache (qil/model.py:52-57, qil/cache.py:93-94).  Heads are 128 wide,
+// so every 128-column half of an output tile is one whole head and one thread holds a token's head in
+// registers.  The arithmetic and its rounding points are those of rope_kv.cu's bfloat16 kernel: the
+// product rounded to bfloat16 first, sums of squares and the normalising factor in float32, the normed
+// value rounded before the weight multiplies it, every product and sum of the rotation rounded by itself.
+struct TcQkvTail {
+    bf16* q_out;                 // [tokens, n_q_heads, 128]; null: the ordinary epilogue
+    bf16* pages;                 // one layer's cache: [page][2][n_kv_heads][page_size][128]
+    const float* rope;           // [rope_rows][128]: 64 cosines then 64 sines per position; null: no rotation
+    const bf16* q_norm;          // [128] or null
+    const bf16* k_norm;
+    const int* positions;        // [tokens]
+    const int* token_row;        // [tokens] block-table row
+    const int* block_table;
+    float eps;
+    int table_stride, rope_rows, n_q_heads, n_kv_heads, page_size, num_pages;
+};
+
+__device__ __forceinline__ void tc_store_qkv_head(unsigned taddr, int m, int M, int head, const TcQkvTail& t,
+                                                  const bf16* __restrict__ bias) {
+    typedef __nv_bfloat162 bf2;
+    // The head as 64 packed pairs (elements 2i, 2i + 1), rounded to bfloat16 as the product's output is.
+    // Packed arithmetic from here on: one instruction per two values, and half the registers; the single
+    // epilogue warp of a scheduler runs one dependent instruction after the other, so their number is
+    // what the epilogue costs.
+    bf2 pk[64];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        float part[32];
+        __syncwarp();                              // the load is a warp-wide instruction: every lane takes part
+        tmem_load_32(taddr + c * 32, part);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float x = part[2 * i], y = part[2 * i + 1];
+            if (bias != nullptr) {
+                const float2 b = __bfloat1622float2(*reinterpret_cast<const bf2*>(bias + head * 128 + c * 32 + 2 * i));
+                x += b.x; y += b.y;
+            }
+            pk[c * 16 + i] = __floats2bfloat162_rn(x, y);
+        }
+    }
+    if (m >= M) return;
+    const bool is_q = head < t.n_q_heads;
+    const bool is_k = !is_q && head < t.n_q_heads + t.n_kv_heads;
+    const bf16* norm_w = is_q ? t.q_norm : (is_k ? t.k_norm : nullptr);
+    if (norm_w != nullptr) {
+        float sq = 0.f;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+            const float2 f = __bfloat1622float2(pk[i]);
+            sq = fmaf(f.x, f.x, sq);
+            sq = fmaf(f.y, f.y, sq);
+        }
+        const float scale = rsqrtf(sq / 128.0f + t.eps);
+        const bf2* w2 = reinterpret_cast<const bf2*>(norm_w);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+            const float2 f = __bfloat1622float2(pk[i]);
+            pk[i] = __hmul2_rn(__floats2bfloat162_rn(f.x * scale, f.y * scale), w2[i]);
+        }
+    }
+    const int pos = t.positions[m];
+    if ((is_q || is_k) && t.rope != nullptr) {
+        const int row = (pos >= t.rope_rows && t.rope_rows > 0) ? t.rope_rows - 1 : pos;
+        const float4* cs = reinterpret_cast<const float4*>(t.rope + (size_t)row * 128);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            // the table holds values already rounded to bfloat16: the conversion is exact
+            const float4 cf = cs[i / 2], sf = cs[16 + i / 2];
+            const bf2 c0 = __floats2bfloat162_rn(cf.x, cf.y), c1 = __floats2bfloat162_rn(cf.z, cf.w);
+            const bf2 s0 = __floats2bfloat162_rn(sf.x, sf.y), s1 = __floats2bfloat162_rn(sf.z, sf.w);
+            const bf2 lo0 = pk[i], lo1 = pk[i + 1], hi0 = pk[32 + i], hi1 = pk[32 + i + 1];
+            // every product and sum rounds by itself (the _rn forms are never contracted into fused multiply-adds)
+            pk[i] = __hsub2_rn(__hmul2_rn(lo0, c0), __hmul2_rn(hi0, s0));
+            pk[i + 1] = __hsub2_rn(__hmul2_rn(lo1, c1), __hmul2_rn(hi1, s1));
+            pk[32 + i] = __hadd2_rn(__hmul2_rn(lo0, s0), __hmul2_rn(hi0, c0));
+            pk[32 + i + 1] = __hadd2_rn(__hmul2_rn(lo1, s1), __hmul2_rn(hi1, c1));
+        }
+    }
+    bf16* dst;
+    if (is_q) {
+        dst = t.q_out + ((size_t)m * t.n_q_heads + head) * 128;
+    } else {
+        const int kv_head = is_k ? head - t.n_q_heads : head - t.n_q_heads - t.n_kv_heads;
+        const int page = t.block_table[(size_t)t.token_row[m] * t.table_stride + pos / t.page_size];
+        if (page < 0 || page >= t.num_pages) return;        // never write outside the pool
+        dst = t.pages + ((((size_t)page * 2 + (is_k ? 0 : 1)) * t.n_kv_heads + kv_head) * t.page_size + pos % t.page_size) * 128;
+    }
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+        uint4 packed;
+        packed.x = *reinterpret_cast<const unsigned*>(&pk[4 * q]);
+        packed.y = *reinterpret_cast<const unsigned*>(&pk[4 * q + 1]);
+        packed.z = *reinterpret_cast<const unsigned*>(&pk[4 * q + 2]);
+        packed.w = *reinterpret_cast<const unsigned*>(&pk[4 * q + 3]);
+        *reinterpret_cast<uint4*>(dst + q * 8) = packed;
+    }
+}
+
 // One warp's quarter (32 rows) of a finished 128 x 256 accumulator: tcgen05.ld 32 columns at a time,
 // epilogue, bfloat16 stores.  m is this lane's output row, n0 the tile's first output column.
 __device__ __forceinline__ void tc_store_accumulator(unsigned taddr, int m, int n0, int M, int N, int silu_pairs,
@@ -180,7 +281,7 @@ struct TcShared {
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const bf16* __restrict__ bias, const bf16* residual, bf16* out,
-               int M, int N, int K, int silu_pairs, int* error_word) {
+               int M, int N, int K, int silu_pairs, int* error_word, const TcQkvTail tail) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     TcShared* sh = reinterpret_cast<TcShared*>(tiles + TC_STAGES * TC_STAGE_BYTES);
@@ -270,7 +371,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const int m = m0 + quarter * 32 + lane;
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)acc * TC_BN;
-            tc_store_accumulator(taddr, m, n0, M, N, silu_pairs, bias, residual, out);
+            if (tail.q_out != nullptr) {
+#pragma unroll 1
+                for (int h = 0; h < TC_BN / 128; ++h)
+                    if (n0 + h * 128 < N) tc_store_qkv_head(taddr + h * 128, m, M, (n0 + h * 128) / 128, tail, bias);
+            } else {
+                tc_store_accumulator(taddr, m, n0, M, N, silu_pairs, bias, residual, out);
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
@@ -361,7 +468,7 @@ __device__ __forceinline__ unsigned umma_idesc_pair() {
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const bf16* __restrict__ bias, const bf16* residual, bf16* out,
-                    int M, int N, int K, int silu_pairs, int* error_word) {
+                    int M, int N, int K, int silu_pairs, int* error_word, const TcQkvTail tail) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Tc2Shared* sh = reinterpret_cast<Tc2Shared*>(tiles + T2_STAGES * T2_STAGE_BYTES);
@@ -451,7 +558,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_after();
             const int m = m0 + quarter * 32 + lane;
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)acc * TC_BN;
-            tc_store_accumulator(taddr, m, n0, M, N, silu_pairs, bias, residual, out);
+            if (tail.q_out != nullptr) {
+#pragma unroll 1
+                for (int h = 0; h < TC_BN / 128; ++h)
+                    if (n0 + h * 128 < N) tc_store_qkv_head(taddr + h * 128, m, M, (n0 + h * 128) / 128, tail, bias);
+            } else {
+                tc_store_accumulator(taddr, m, n0, M, N, silu_pairs, bias, residual, out);
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&sh->acc_empty[acc]), 0));
@@ -502,10 +615,9 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
 
 extern "C" int qil_gemm_tc_min_rows() { return 17; }
 
-// error_word: a device int the caller zeroes once and reads after synchronising; non-zero means a
-// bounded wait inside the kernel ran out (1-2 producer, 3-4 MMA issuer, 5 epilogue).
-extern "C" int qil_gemm_tc(const void* a, const void* w, const void* bias, const void* residual, void* out,
-                           int M, int N, int K, int silu_pairs, int sm_count, int* error_word, cudaStream_t stream) {
+static int launch_gemm_tc(const void* a, const void* w, const void* bias, const void* residual, void* out,
+                          int M, int N, int K, int silu_pairs, int sm_count, int* error_word, const TcQkvTail& tail,
+                          cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8) QIL_REFUSE("gemm_tc: K %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
     if (N % 8) QIL_REFUSE("gemm_tc: N %d must be a multiple of 8", N);
@@ -549,12 +661,46 @@ extern "C" int qil_gemm_tc(const void* a, const void* w, const void* bias, const
         const int pair_tiles = ((M + 255) / 256) * ((N + TC_BN - 1) / TC_BN);
         const int pairs = pair_tiles < pairs_resident ? pair_tiles : pairs_resident;
         gemm_tc_pair_kernel<<<2 * pairs, 192, smem_pair, stream>>>(map_a, map_w, (const bf16*)bias, (const bf16*)residual,
-                                                                   (bf16*)out, M, N, K, silu_pairs, error_word);
+                                                                   (bf16*)out, M, N, K, silu_pairs, error_word, tail);
         QIL_CHECK_LAUNCH();
     }
     const int n_tiles = ((M + TC_BM - 1) / TC_BM) * ((N + TC_BN - 1) / TC_BN);
     const int blocks = n_tiles < sm_count ? n_tiles : sm_count;
     gemm_tc_kernel<<<blocks, 192, smem, stream>>>(map_a, map_w, (const bf16*)bias, (const bf16*)residual, (bf16*)out,
-                                                  M, N, K, silu_pairs, error_word);
+                                                  M, N, K, silu_pairs, error_word, tail);
     QIL_CHECK_LAUNCH();
+}
+
+// error_word: a device int the caller zeroes once and reads after synchronising; non-zero means a
+// bounded wait inside the kernel ran out (1-2 producer, 3-4 MMA issuer, 5 epilogue).
+extern "C" int qil_gemm_tc(const void* a, const void* w, const void* bias, const void* residual, void* out,
+                           int M, int N, int K, int silu_pairs, int sm_count, int* error_word, cudaStream_t stream) {
+    TcQkvTail none = {};
+    return launch_gemm_tc(a, w, bias, residual, out, M, N, K, silu_pairs, sm_count, error_word, none, stream);
+}
+
+// The stacked query/key/value projection of heads of 128 with its tail fused (see TcQkvTail): w is
+// [(n_q_heads + 2 n_kv_heads) * 128, K] (queries, then keys, then values; n_kv_heads may be 0 for a layer
+// that reads another layer's cache), q_out [M, n_q_heads * 128], pages one layer of the cache.  rope
+// float32 [rope_rows, 128] (cosines then sines, values representable in bfloat16) or null; q_norm, k_norm
+// bfloat16 [128] or null; positions, token_row int32 [M]; block_table int32 rows of table_stride.
+extern "C" int qil_gemm_tc_qkv(const void* a, const void* w, const void* bias, void* q_out, void* pages,
+                               const float* rope, int rope_rows, const void* q_norm, const void* k_norm, float eps,
+                               const int* positions, const int* token_row, const int* block_table, int table_stride,
+                               int n_q_heads, int n_kv_heads, int page_size, int num_pages,
+                               int M, int K, int sm_count, int* error_word, cudaStream_t stream) {
+    if (n_q_heads <= 0 || n_kv_heads < 0) QIL_REFUSE("gemm_tc_qkv: %d query heads, %d kv heads", n_q_heads, n_kv_heads);
+    if (q_out == nullptr || positions == nullptr) QIL_REFUSE("gemm_tc_qkv: needs the query buffer and the positions");
+    if (n_kv_heads > 0 && (pages == nullptr || token_row == nullptr || block_table == nullptr || page_size <= 0 || num_pages <= 0))
+        QIL_REFUSE("gemm_tc_qkv: keys and values need the cache, the block table and the tokens' rows");
+    if (((uintptr_t)q_out | (uintptr_t)pages | (uintptr_t)rope | (uintptr_t)q_norm | (uintptr_t)k_norm) & 15)
+        QIL_REFUSE("gemm_tc_qkv: buffers must be 16-byte aligned");
+    TcQkvTail tail = {};
+    tail.q_out = (bf16*)q_out; tail.pages = (bf16*)pages; tail.rope = rope; tail.rope_rows = rope_rows;
+    tail.q_norm = (const bf16*)q_norm; tail.k_norm = (const bf16*)k_norm; tail.eps = eps;
+    tail.positions = positions; tail.token_row = token_row; tail.block_table = block_table;
+    tail.table_stride = table_stride; tail.n_q_heads = n_q_heads; tail.n_kv_heads = n_kv_heads;
+    tail.page_size = page_size > 0 ? page_size : 1; tail.num_pages = num_pages;
+    const int N = (n_q_heads + 2 * n_kv_heads) * 128;
+    return launch_gemm_tc(a, w, bias, nullptr, q_out, M, N, K, 0, sm_count, error_word, tail, stream);
 }

@@ -170,7 +170,7 @@ qk_norm_rope_store_bf16_kernel(
                 const bf2* w2 = reinterpret_cast<const bf2*>(norm_w);
                 auto normed = [&](bf2 v, int j) {     // round(x * scale) in float32, then times the weight in bfloat16
                     const float2 f = __bfloat1622float2(v);
-                    return __hmul2(__floats2bfloat162_rn(f.x * scale, f.y * scale), w2[j / 2]);
+                    return __hmul2_rn(__floats2bfloat162_rn(f.x * scale, f.y * scale), w2[j / 2]);
                 };
 #pragma unroll
                 for (int i = 0; i < RUNS; ++i) {
@@ -202,9 +202,11 @@ qk_norm_rope_store_bf16_kernel(
                         const float2 cf = *reinterpret_cast<const float2*>(cs + j);
                         const float2 sf = *reinterpret_cast<const float2*>(cs + half + j);
                         const bf2 c = __floats2bfloat162_rn(cf.x, cf.y), sn = __floats2bfloat162_rn(sf.x, sf.y);
-                        // each product and the sum round separately, as elementwise tensor code does
-                        out2[j / 2] = __hsub2(__hmul2(lo[u][i], c), __hmul2(hi[u][i], sn));
-                        out2[(j + half) / 2] = __hadd2(__hmul2(lo[u][i], sn), __hmul2(hi[u][i], c));
+                        // each product and the sum round separately, as elementwise tensor code does: the _rn
+                        // forms, because the plain ones may be contracted into fused multiply-adds, which round
+                        // once where the reference rounds twice (one value in five then differs in its last bit)
+                        out2[j / 2] = __hsub2_rn(__hmul2_rn(lo[u][i], c), __hmul2_rn(hi[u][i], sn));
+                        out2[(j + half) / 2] = __hadd2_rn(__hmul2_rn(lo[u][i], sn), __hmul2_rn(hi[u][i], c));
                     }
                 }
             }

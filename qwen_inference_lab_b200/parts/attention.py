@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import gemm_tc, ops
 from .base import KVCacheSpec, Mixer, Param
 from .linear import Linear, StackedLinear
 
@@ -78,10 +78,22 @@ class GroupedQueryAttention(Mixer):
         the block's un-normed input and the first projection applies the norm."""
         n = x.shape[0]
         n_kv = 0 if self.reads_shared_cache else self.n_kv_heads
-        qkv = self.qkv.forward(ctx, x, norm=norm)
         q = ctx.empty((n, self.n_q_heads * self.head_dim))
         table = self.position.table if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
+        q_norm = self.q_norm.data if self.q_norm is not None else None
+        k_norm = self.k_norm.data if self.k_norm is not None else None
+        if gemm_tc.qkv_tail_usable(x, self.qkv._weight(), self.head_dim, rotary_dim, (q_norm, k_norm), cache.pages):
+            # long prompt portions: one tcgen05 kernel projects, norms, rotates and writes the pages
+            if norm is not None:
+                x = norm.forward(ctx, x)
+            gemm_tc.gemm_tc_qkv(x, self.qkv._weight(), self.qkv._bias(), q, cache.pages, table, q_norm, k_norm,
+                                self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, ctx.positions,
+                                ctx.token_row, cache.block_table, self.n_q_heads, n_kv, cache.page_size)
+            attended = ctx.empty((n, self.n_q_heads * self.head_dim))
+            self._attend(ctx, q, cache, attended)
+            return self.out.forward(ctx, attended, residual=residual)
+        qkv = self.qkv.forward(ctx, x, norm=norm)
         ops.qk_norm_rope_store(
             qkv, q, cache.pages, self.q_norm.data if self.q_norm is not None else None,
             self.k_norm.data if self.k_norm is not None else None,

@@ -443,6 +443,77 @@ def test_gemm_tensor_memory_with_gate_epilogue(m, inner, k):
     gemm_tc.check()
 
 
+@pytest.mark.parametrize("m,k,n_q,n_kv,page,bias,norms,rope", [
+    (100, 136, 3, 1, 8, True, True, True),       # the one-block kernel, an odd number of heads
+    (300, 256, 4, 2, 16, False, True, True),     # pairs of SMs; the last tile of tokens is partly empty
+    (700, 520, 6, 2, 64, True, False, True),
+    (260, 64, 2, 0, 16, False, True, False),     # a layer without keys and values of its own, no rotation
+])
+def test_gemm_tensor_memory_with_the_qkv_tail(m, k, n_q, n_kv, page, bias, norms, rope):
+    """Projection, per-head norm, rotation and the write into shuffled pages in one kernel, against the same
+    steps as separate kernels (product, then the norm/rotation/store kernel) and against plain float32."""
+    from qwen_inference_lab_b200.kernels import gemm_tc
+    from qwen_inference_lab_b200.parts.rotary import rotary_table
+    torch.manual_seed(15)
+    d, eps = 128, 1e-5
+    heads = n_q + 2 * n_kv
+    a = torch.randn(m, k).to(torch.bfloat16).cuda()
+    w = (torch.randn(heads * d, k) * 0.1).to(torch.bfloat16).cuda()
+    b = (torch.randn(heads * d) * 0.5).to(torch.bfloat16).cuda() if bias else None
+    q_norm = (1 + 0.3 * torch.randn(d)).to(torch.bfloat16).cuda() if norms else None
+    k_norm = (1 + 0.3 * torch.randn(d)).to(torch.bfloat16).cuda() if norms else None
+    table = rotary_table(d, 10000.0, 2048, torch.bfloat16).cuda() if rope else None
+    # two requests: the first fills positions 37.. of block-table row 1, the second 0.. of row 0
+    first = m * 2 // 3
+    positions = torch.cat([torch.arange(37, 37 + first), torch.arange(0, m - first)]).to(torch.int32).cuda()
+    token_row = torch.cat([torch.full((first,), 1), torch.full((m - first,), 0)]).to(torch.int32).cuda()
+    pages_per_request = (37 + first + page - 1) // page + 1
+    num_pages = 2 * pages_per_request + 3
+    block_table = torch.randperm(num_pages)[:2 * pages_per_request].view(2, pages_per_request).to(torch.int32).cuda()
+    def run(fused):
+        q = torch.full((m, n_q * d), float("nan"), dtype=torch.bfloat16).cuda()
+        pages = torch.full((num_pages, 2, max(n_kv, 1), page, d), float("nan"), dtype=torch.bfloat16).cuda()
+        if fused:
+            gemm_tc.gemm_tc_qkv(a, w, b, q, pages if n_kv else None, table, q_norm, k_norm, eps, positions, token_row,
+                                block_table, n_q, n_kv, page)
+        else:
+            qkv = gemm_tc.gemm_tc(a, w, bias=b)
+            ops().qk_norm_rope_store(qkv, q, pages, q_norm, k_norm, eps, table, d if rope else 0, positions, token_row,
+                                     block_table, n_q, n_kv, d, page)
+        torch.cuda.synchronize()
+        gemm_tc.check()
+        return q, pages
+    q_fused, pages_fused = run(True)
+    q_split, pages_split = run(False)
+    assert not torch.isnan(q_fused).any()
+    # the same slots written, nothing else touched
+    assert torch.equal(torch.isnan(pages_fused), torch.isnan(pages_split))
+    # the two differ only where a normalising factor differs in its last bit and a value sits on a rounding edge
+    scale = 4.0
+    close(q_fused, q_split, torch.bfloat16, scale=scale)
+    close(torch.nan_to_num(pages_fused), torch.nan_to_num(pages_split), torch.bfloat16, scale=scale)
+    assert (q_fused != q_split).float().mean() < 0.02
+    # and against plain float32 arithmetic on the bfloat16-rounded product
+    qkv = (a.float() @ w.float().t() + (b.float() if bias else 0)).to(torch.bfloat16).float().view(m, heads, d).cpu()
+    def norm_rotate(x, weight):
+        if weight is not None:
+            x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.float().cpu()
+        if rope:
+            cs = table.cpu()[positions.cpu().long()]
+            c, s_ = cs[:, None, :d // 2], cs[:, None, d // 2:]
+            lo, hi = x[..., :d // 2], x[..., d // 2:]
+            x = torch.cat([lo * c - hi * s_, lo * s_ + hi * c], dim=-1)
+        return x
+    close(q_fused.view(m, n_q, d), norm_rotate(qkv[:, :n_q], q_norm), torch.bfloat16, scale=scale)
+    if n_kv:
+        keys = norm_rotate(qkv[:, n_q:n_q + n_kv], k_norm)
+        for token in (0, first - 1, first, m - 1):
+            pos, row = int(positions[token]), int(token_row[token])
+            page_id = int(block_table[row, pos // page])
+            close(pages_fused[page_id, 0, :, pos % page], keys[token], torch.bfloat16, scale=scale)
+            close(pages_fused[page_id, 1, :, pos % page], qkv[token, n_q + n_kv:], torch.bfloat16, scale=scale)
+
+
 TENSOR_MEMORY_ATTENTION_CASES = [
     # n_q, n_kv, lengths, chunk starts (chunk lengths are multiples of 128), page
     (1, 1, [128], [0], 16),
