@@ -3,7 +3,7 @@ import pytest
 import torch
 
 from tests import harness
-from tests.tiny_configs import TINY_A, TINY_B, TINY_C
+from tests.tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
 
@@ -11,6 +11,7 @@ CASES = {
     "A": dict(cfg=TINY_A, seed=0, page_size=4, lengths=(5, 17, 33, 90)),
     "B": dict(cfg=TINY_B, seed=1, page_size=8, lengths=(1, 9, 31, 64, 100, 150)),
     "C": dict(cfg=TINY_C, seed=2, page_size=16, lengths=(40, 3, 130, 70)),
+    "D": dict(cfg=TINY_D, seed=3, page_size=16, lengths=(700, 300, 1100)),
 }
 SCHEDULES = {
     "whole": harness.whole_schedule,
@@ -71,3 +72,29 @@ def test_recorded_steps_survive_a_step_that_outgrows_the_runner(folders):
     expected = harness.plain_rows(requests, weights, cfg, torch.float32)
     yardstick = harness.plain_rows(requests, weights, cfg, torch.bfloat16)
     harness.assert_rows_close(actual, expected, torch.bfloat16, "after the buffers grew", yardstick)
+
+
+def test_long_prompts_take_the_tensor_memory_kernels(folders, monkeypatch):
+    """Heads of 128 and whole prompts of several hundred tokens: the step must go through the tcgen05
+    product with the fused q/k/v tail, the tcgen05 gate/up product and the tcgen05 attention (the replay
+    cases above check their results; this checks that it is those kernels that produced them)."""
+    from qwen_inference_lab_b200.kernels import attention_tc, gemm_tc
+    calls = {"qkv": 0, "gate_up": 0, "attention": 0}
+    def counted(module, name, key):
+        original = getattr(module, name)
+        def wrapper(*args, **kwargs):
+            calls[key] += 1
+            return original(*args, **kwargs)
+        monkeypatch.setattr(module, name, wrapper)
+    counted(gemm_tc, "gemm_tc_qkv", "qkv")
+    counted(gemm_tc, "gemm_tc", "gate_up")
+    counted(attention_tc, "prefill", "attention")
+    folder, weights, requests = folders["D"]
+    _, cache, runner = harness.build_engine_parts(folder, torch.bfloat16, num_pages=80, page_size=16)
+    harness.run_schedule(runner, cache, harness.whole_schedule(requests))
+    layers = TINY_D["num_hidden_layers"]
+    assert calls["qkv"] == 2 * layers            # the prompts of 700 and 1100 tokens; 300 is below the tail's threshold
+    assert calls["gate_up"] == 3 * layers and calls["attention"] == 3 * layers
+    torch.cuda.synchronize()
+    gemm_tc.check()
+    attention_tc.check()

@@ -22,6 +22,14 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size
               head_dim=48, max_position_embeddings=640, rope_theta=50000.0, rms_norm_eps=3e-6,
               attention_bias=True, tie_word_embeddings=False, eos_token_id=3)
 
+# heads of 128 and a width that the tcgen05 kernels take: long prompts of this one go through the
+# tensor-memory product (pairs of SMs from 256 tokens on), its fused q/k/v tail (from 512 tokens on)
+# and the tensor-memory attention (whole tiles of 128 tokens)
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=1500, hidden_size=192,
+              intermediate_size=328, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2,
+              head_dim=128, max_position_embeddings=2048, rope_theta=1000000.0, rms_norm_eps=1e-6,
+              attention_bias=True, tie_word_embeddings=True, eos_token_id=None)
+
 
 def typed(cfg: dict) -> Qwen3Config:
     return Qwen3Config.from_dict(cfg)
