@@ -254,7 +254,7 @@ class OursBench:
         prompt_len = context - 1
         pages = batch * ((prompt_len + new_tokens + PAGE_SIZE - 1) // PAGE_SIZE + 1)
         engine = Engine(self.model, num_pages=pages, page_size=PAGE_SIZE, token_budget=2048, prefill_chunk=2048,
-                        max_active=batch)
+                        max_active=batch, overlap=True)       # a step ahead of the host, as generate() runs
         generator = torch.Generator().manual_seed(3)
         for _ in range(batch):
             prompt = torch.randint(0, self.cfg["vocab_size"], (prompt_len,), generator=generator).tolist()

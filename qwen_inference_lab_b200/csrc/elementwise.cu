@@ -224,6 +224,25 @@ extern "C" int qil_add_inplace(void* x, const void* y, long long total, int act_
     QIL_CHECK_LAUNCH();
 }
 
+// ---------------------------------------------------------------- token ids that are still on the device
+// token_ids[pairs[2i]] = source[pairs[2i + 1]]: a step may be queued before the host has read the tokens
+// that the step before it sampled; their places in the step's token list are filled in here, on the
+// stream, from the sampler's device buffer.  A source index outside [0, n_source) leaves the place as it is.
+__global__ void feed_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ pairs, int count,
+                                   const int* __restrict__ source, int n_source, int n_tokens) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const int dst = pairs[2 * i], src = pairs[2 * i + 1];
+    if (dst >= 0 && dst < n_tokens && src >= 0 && src < n_source) token_ids[dst] = source[src];
+}
+
+extern "C" int qil_feed_tokens(int* token_ids, const int* pairs, int count, const int* source, int n_source,
+                               int n_tokens, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    feed_tokens_kernel<<<(count + 127) / 128, 128, 0, stream>>>(token_ids, pairs, count, source, n_source, n_tokens);
+    QIL_CHECK_LAUNCH();
+}
+
 // ---------------------------------------------------------------- dtype cast (src dtype -> dst dtype)
 template <typename T, typename W>
 __global__ void cast_kernel(const W* __restrict__ src, T* __restrict__ dst, size_t total) {

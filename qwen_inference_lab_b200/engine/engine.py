@@ -8,6 +8,14 @@ decode tokens (qil/engine.py:59-86), a step here is one batch of everything that
 was planned.  If a step fails, every request in it is retired as ``failed`` and its
 pages are freed, since any of them may hold partly written pages
 (qil/engine.py:87-93); requests outside the batch go on.
+
+With ``overlap=True`` the engine runs one step ahead of the host: a step is planned and queued while
+the step before it is still on the GPU, the tokens that step sampled are fed to the new one on the
+device (``StepEntry.feed``), and only then does the host wait for them, append them, and retire what
+finished.  The GPU never waits for the host's planning.  ``step`` then returns the events of the step
+before the one it queued; a request that ended with an end-of-sequence token has by then one more
+token queued, which is computed and dropped.  ``generate`` and the command line use this mode;
+``Engine(...)`` defaults to the reference's behaviour (a step's own events).
 """
 from __future__ import annotations
 
@@ -17,13 +25,15 @@ from ..cache import CacheManager
 from ..kernels import attention_tc, gemm_tc
 from ..sampling import Sampler
 from .scheduler import Request, Scheduler
-from .step import StepEntry, StepRunner
+from .step import PENDING, StepEntry, StepRunner
 
 
 class Engine:
     def __init__(self, model, *, num_pages=256, page_size=16, token_budget=128, prefill_chunk=64,
-                 max_active=4, clock=perf_counter, seed=0, use_graphs=True):
+                 max_active=4, clock=perf_counter, seed=0, use_graphs=True, overlap=False):
         self.model = model
+        self.overlap = bool(overlap)
+        self._queued = None           # the step that is on the GPU and whose tokens the host has not read
         self.clock = clock
         self.seed = int(seed)
         self.next_id = 0
@@ -64,44 +74,93 @@ class Engine:
         return request_id
 
     def step(self) -> list:
-        """Run one planned batch; returns events ``dict(request_id, token_id, timestamp_s, finished)``."""
+        """Run one planned batch; returns events ``dict(request_id, token_id, timestamp_s, finished)``:
+        of this batch, or with ``overlap`` of the batch queued by the call before."""
+        if self.overlap:
+            return self._step_ahead()
         plan = self.scheduler.plan()
+        try:
+            queued = self._queue(plan, None)
+        except Exception as error:
+            self._fail(plan, error)
+            raise
+        return self._collect(queued) if queued is not None else []
+
+    def _step_ahead(self) -> list:
+        before = self._queued
+        plan = self.scheduler.plan()
+        try:
+            self._queued = self._queue(plan, before)
+        except Exception as error:
+            self._queued = None
+            if before is not None:
+                self._collect(before, quiet=True)       # its tokens are kept; the error below is the news
+            self._fail(plan, error)
+            raise
+        return self._collect(before) if before is not None else []
+
+    def _queue(self, plan, before):
+        """Queue a plan's step and the choice of its tokens; nothing waits.  ``before``: the step whose
+        tokens are still on the device (requests with a pending token take it from there)."""
         if not plan:
-            return []
+            return None
         requests = self.scheduler.requests
         entries, ready = [], []
         for work in plan:
             request = requests[work.request_id]
             done = work.start + len(work.tokens) == request.input_length
-            entries.append(StepEntry(work.request_id, work.tokens, [len(work.tokens) - 1] if done else []))
+            feed = None
+            if work.tokens[-1] == PENDING:
+                feed = before["slot"][request.id]
+            entries.append(StepEntry(work.request_id, work.tokens, [len(work.tokens) - 1] if done else [], feed))
             if done:
                 ready.append(request)
+        source = before["ticket"].tokens if before is not None and before["ticket"] is not None else None
+        logits = self.runner.run(entries, source)
+        ticket = None
+        if ready:
+            ticket = self.sampler.begin(logits, [r.temperature for r in ready], [r.seed for r in ready],
+                                        [len(r.output) + r.pending for r in ready])
+        for work in plan:
+            requests[work.request_id].computed = work.start + len(work.tokens)
+        for request in ready:
+            request.pending += 1          # 2 for a moment when running ahead: this step's and the one before's
+        return dict(plan=plan, ready=ready, ticket=ticket, slot={r.id: i for i, r in enumerate(ready)})
+
+    def _fail(self, plan, error):
+        for work in plan:
+            request = self.scheduler.requests[work.request_id]
+            if request.state == "active":
+                request.error = str(error)
+                request.pending = 0
+                self.scheduler.retire(work.request_id, "failed", "error")
+
+    def _collect(self, queued, quiet=False) -> list:
+        """Wait for a queued step's tokens; append them, retire what finished, return the events."""
+        plan, ready = queued["plan"], queued["ready"]
+        requests = self.scheduler.requests
         try:
-            logits = self.runner.run(entries)
-            tokens = []
-            if ready:
-                tokens = self.sampler.choose(logits, [r.temperature for r in ready], [r.seed for r in ready],
-                                             [len(r.output) for r in ready])
+            tokens = self.sampler.finish(queued["ticket"]) if queued["ticket"] is not None else []
             if sum(len(work.tokens) for work in plan) >= gemm_tc.MIN_ROWS:
                 gemm_tc.check()      # the tensor-memory kernels' bounded waits report through error words
                 attention_tc.check()
         except Exception as error:
-            for work in plan:
-                requests[work.request_id].error = str(error)
-                self.scheduler.retire(work.request_id, "failed", "error")
+            self._fail(plan, error)
+            if quiet:
+                return []
             raise
         self.counters["steps"] += 1
-        events, emitted = [], dict(zip((r.id for r in ready), tokens))
         for work in plan:
-            request = requests[work.request_id]
             count = len(work.tokens)
             self.counters["tokens"] += count
-            self.counters["prefill_tokens" if work.start < len(request.prompt) else "decode_tokens"] += count
-            request.computed = work.start + count
-            if request.id not in emitted:
-                continue
-            token = emitted[request.id]
+            prompt_length = len(requests[work.request_id].prompt)
+            self.counters["prefill_tokens" if work.start < prompt_length else "decode_tokens"] += count
+        events = []
+        for request, token in zip(ready, tokens):
+            if request.state != "active" or not request.pending:
+                continue                # cancelled, failed or finished since: the token is dropped
             observed = self.clock()
+            request.pending -= 1
             request.output.append(token)
             request.token_times_s.append(observed)
             reason = "eos" if token in request.eos else (
@@ -129,7 +188,7 @@ class Engine:
 
     @property
     def idle(self) -> bool:
-        return self.scheduler.idle
+        return self.scheduler.idle and self._queued is None
 
     def generate(self, prompts, *, max_new_tokens=64, ignore_eos=False, temperature=0.0, seed=None) -> list:
         if not self.idle:
@@ -140,8 +199,12 @@ class Engine:
                 request_ids.append(self.submit(
                     prompt, max_new_tokens=max_new_tokens, ignore_eos=ignore_eos, temperature=temperature,
                     seed=None if seed is None else seed + index))
-            while not self.idle:
-                self.step()
+            ahead, self.overlap = self.overlap, True       # nobody reads the events here: run a step ahead
+            try:
+                while not self.idle:
+                    self.step()
+            finally:
+                self.overlap = ahead
         except Exception:
             for request_id in request_ids:
                 self.cancel(request_id)
@@ -151,3 +214,6 @@ class Engine:
     def close(self) -> None:
         for request_id in list(self.scheduler.active) + list(self.scheduler.waiting):
             self.cancel(request_id)
+        if self._queued is not None:
+            queued, self._queued = self._queued, None
+            self._collect(queued, quiet=True)

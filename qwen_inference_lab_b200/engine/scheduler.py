@@ -34,6 +34,10 @@ class Request:
     output: list = field(default_factory=list)
     token_times_s: list = field(default_factory=list)
     computed: int = 0
+    # output tokens that queued steps have sampled and the host has not read yet: they count as input
+    # already, so the next step can be planned and queued before they are known (at most one while a
+    # step is planned)
+    pending: int = 0
     state: str = "waiting"            # waiting, active, completed, cancelled, failed
     finish_reason: str | None = None
     error: str | None = None
@@ -44,16 +48,26 @@ class Request:
 
     @property
     def input_length(self):
-        return len(self.prompt) + len(self.output)
+        return len(self.prompt) + len(self.output) + self.pending
 
     def input_slice(self, start, count):
-        """``input_tokens[start:start + count]`` without building the whole list."""
+        """``input_tokens[start:start + count]`` without building the whole list; a pending token's
+        place holds PENDING (-1)."""
         split = len(self.prompt)
+        known = split + len(self.output)
+        if start + count > known:           # reaches into the pending token
+            head = self.input_slice(start, known - start) if start < known else []
+            return head + [-1] * (start + count - max(start, known))
         if start >= split:
             return self.output[start - split:start - split + count]
         if start + count <= split:
             return self.prompt[start:start + count]
         return self.prompt[start:] + self.output[:start + count - split]
+
+    @property
+    def ends_with_pending(self):
+        """The pending token is the request's last: it needs no further step."""
+        return self.pending > 0 and len(self.output) + self.pending >= self.max_new_tokens
 
     @property
     def cache_limit(self):
@@ -104,6 +118,9 @@ class Scheduler:
                 break
             request_id = self.active.popleft()
             request = self.requests[request_id]
+            if request.ends_with_pending:
+                self.active.append(request_id)      # retires when its last token has been read
+                continue
             chunk = self.prefill_chunk if request.computed < len(request.prompt) else 1
             count = min(chunk, remaining, request.input_length - request.computed)
             if count <= 0:
@@ -111,7 +128,7 @@ class Scheduler:
             work.append(Work(request_id, request.computed, request.input_slice(request.computed, count)))
             remaining -= count
             self.active.append(request_id)
-        if not work and self.waiting:
+        if not work and self.waiting and not self.active:
             raise RuntimeError("no runnable request despite an empty active set")
         return work
 

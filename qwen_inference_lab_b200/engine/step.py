@@ -31,11 +31,17 @@ class StepError(ValueError):
     """A batch that cannot run: unknown request, bad token, position beyond the context..."""
 
 
+PENDING = -1      # in ``StepEntry.tokens``: a token that is still on the device (see ``StepEntry.feed``)
+
+
 @dataclass
 class StepEntry:
     request_id: object
     tokens: list
     want: list = field(default_factory=list)   # indices into ``tokens`` whose logits are returned
+    # When the last of ``tokens`` is PENDING: its index in the device buffer given to ``run`` as
+    # ``token_source`` (the tokens that the step before sampled and the host has not read yet).
+    feed: int | None = None
 
 
 def _align4(n):
@@ -85,8 +91,11 @@ class StepRunner:
             tokens = entry.tokens
             if len(tokens) == 0:
                 raise StepError(f"request {entry.request_id!r} brings no tokens")
-            if any(type(t) is not int or not 0 <= t < vocab for t in tokens):
+            known = tokens if entry.feed is None else tokens[:-1]
+            if any(type(t) is not int or not 0 <= t < vocab for t in known):
                 raise StepError(f"request {entry.request_id!r}: token ids must be integers in [0, {vocab})")
+            if entry.feed is not None and (tokens[-1] != PENDING or type(entry.feed) is not int or entry.feed < 0):
+                raise StepError(f"request {entry.request_id!r}: a fed token must be the last one and marked PENDING")
             start = self.cache.written(entry.request_id)
             if start + len(tokens) > self.model.max_positions:
                 raise StepError(f"request {entry.request_id!r} exceeds the model's {self.model.max_positions} positions")
@@ -97,7 +106,7 @@ class StepRunner:
         """The description of a step in which every request brings one token.  Consecutive decode steps
         of the same requests differ only in the tokens and the positions: the packed vector of the last
         such step is kept and those entries are overwritten."""
-        key = tuple((e.request_id, tuple(e.want)) for e in entries)
+        key = tuple((e.request_id, tuple(e.want), e.feed) for e in entries)
         starts = np.fromiter((self.cache.written(e.request_id) for e in entries), dtype=np.int64, count=len(entries))
         kept = self._single_token_template
         if kept is None or kept[0] != key:
@@ -155,10 +164,15 @@ class StepRunner:
         single = np.nonzero(lens == 1)[0]
         decode_info = np.stack([seg_start[single], starts[single], rows[single], np.zeros_like(single)],
                                axis=1).reshape(-1) if len(single) else np.zeros(0, dtype=np.int64)
+        # places of tokens that are still on the device: (index in the flat batch, index in the source buffer)
+        feed = np.array([v for i, e in enumerate(entries) if e.feed is not None
+                         for v in (seg_start[i] + lens[i] - 1, e.feed)], dtype=np.int64)
+        # "feed" comes last: recorded graphs hold the offsets of the sections before it, which for a step of
+        # single tokens depend on the number of requests only
         sections = [("token_ids", token_ids), ("positions", positions), ("token_row", token_row),
                     ("seg_row", rows), ("seg_start", seg_start), ("seg_len", lens), ("seg_pos0", starts),
                     ("logit_rows", logit_rows), ("tile_info", tile_info), ("decode_info", decode_info),
-                    ("big_tile_info", big_tile_info), ("rest_tile_info", rest_tile_info)]
+                    ("big_tile_info", big_tile_info), ("rest_tile_info", rest_tile_info), ("feed", feed)]
         offsets, total = {}, 0
         for name, values in sections:
             offsets[name] = (total, len(values))
@@ -197,12 +211,13 @@ class StepRunner:
         self._ring.commit()
 
     # ------------------------------------------------------------------ running
-    def run(self, entries) -> torch.Tensor | None:
+    def run(self, entries, token_source=None) -> torch.Tensor | None:
         """Run one step; float32 logits [wanted, vocab] in the order of entries and ``want``.
 
         Pages for the new tokens are taken first, the cache's progress moves after the
         layers have been queued.  On an exception the requests of the batch may hold
         partly written pages: the caller retires them (qil/engine.py:87-93).
+        ``token_source``: int32 on the device, read on the stream for entries with ``feed``.
         """
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
@@ -211,6 +226,13 @@ class StepRunner:
         packed, offsets, host, n, s, max_context = self._describe(entries)
         self.cache.flush_tables()
         self._upload(packed)
+        feed_begin, feed_count = offsets["feed"]
+        if feed_count:
+            if token_source is None:
+                raise StepError("entries with a fed token need the device buffer the tokens come from")
+            begin = offsets["token_ids"][0]
+            ops.feed_tokens(self._meta_dev[begin:begin + n], self._meta_dev[feed_begin:feed_begin + feed_count],
+                            feed_count // 2, token_source)
         all_single = offsets["tile_info"][1] == 0 and offsets["logit_rows"][1] == n \
             and all(e.want == [0] for e in entries)
         if self.use_graphs and all_single and n <= self.graph_max_batch:

@@ -176,6 +176,18 @@ def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=Fals
     return out
 
 
+def feed_tokens(token_ids, pairs, count, source):
+    """token_ids[pairs[2i]] = source[pairs[2i + 1]] for i < count, on the stream (all int32, on the device):
+    fills the places of tokens that the previous step sampled and the host has not read yet."""
+    _need(token_ids, "token_ids", torch.int32, 1); _need(pairs, "pairs", torch.int32, 1)
+    _need(source, "source", torch.int32, 1)
+    if pairs.shape[0] < 2 * count:
+        raise KernelError("feed_tokens: fewer pairs than count")
+    lib = core()
+    _check(lib, lib.qil_feed_tokens(_p(token_ids), _p(pairs), c_int(count), _p(source), c_int(source.shape[0]),
+                                    c_int(token_ids.shape[0]), _stream()), "feed_tokens")
+
+
 def add_inplace(x, y):
     _need(x, "x"); _need(y, "y", x.dtype)
     if x.shape != y.shape:

@@ -18,10 +18,19 @@ class NonFiniteLogits(RuntimeError):
     pass
 
 
+class _Ticket:
+    __slots__ = ("tokens", "host", "event", "rows")
+
+    def __init__(self, tokens, host, event, rows):
+        self.tokens, self.host, self.event, self.rows = tokens, host, event, rows
+
+
 class Sampler:
     def __init__(self, device, max_rows=256):
         self.device = torch.device(device)
         self._views = {}
+        self._async = [None, None]      # two sets of (device pair, pinned pair, its numpy view, event) for begin/finish
+        self._next_slot = 1
         self._allocate(max_rows)
 
     def _allocate(self, rows):
@@ -41,6 +50,40 @@ class Sampler:
             views = (self._result[0, :rows], self._result[1, :rows], self._result[:, :rows], self._host[:, :rows])
             self._views[rows] = views
         return views
+
+    def begin(self, logits, temperatures=None, seeds=None, counters=None):
+        """Queue the choice for every row of ``logits`` and its copy to the host; nothing waits.
+
+        Returns a ticket for ``finish``; ``ticket.tokens`` is the int32 device tensor [R] that holds the
+        chosen ids once the stream gets there (the next step may read it on the stream before the
+        host does).  Two tickets may be open at a time: buffers alternate.
+        """
+        rows = logits.shape[0]
+        slot = self._next_slot = (self._next_slot + 1) % 2
+        pair = self._async[slot]
+        if pair is None or pair[0].shape[1] < rows:
+            size = max(rows, self._result.shape[1])
+            device = torch.zeros((2, size), dtype=torch.int32, device=self.device)
+            host = torch.zeros((2, size), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            pair = self._async[slot] = (device, host, host.numpy(), torch.cuda.Event())
+        device, host, host_numpy, event = pair
+        t = s = c = None
+        if temperatures is not None and any(v > 0 for v in temperatures):
+            t = torch.tensor(list(temperatures), dtype=torch.float32).to(self.device, non_blocking=True)
+            s = torch.tensor([v & 0x7FFFFFFFFFFFFFFF for v in seeds], dtype=torch.int64).to(self.device, non_blocking=True)
+            c = torch.tensor(list(counters), dtype=torch.int64).to(self.device, non_blocking=True)
+        tokens = device[0, :rows]
+        ops.sample_rows(logits, t, s, c, tokens=tokens, nonfinite=device[1, :rows])
+        host[:, :rows].copy_(device[:, :rows], non_blocking=True)
+        event.record()
+        return _Ticket(tokens, host_numpy, event, rows)
+
+    def finish(self, ticket) -> list:
+        """Wait for a ticket's copy; the chosen ids, or NonFiniteLogits."""
+        ticket.event.synchronize()
+        if ticket.host[1, :ticket.rows].any():
+            raise NonFiniteLogits("model returned non-finite logits")
+        return ticket.host[0, :ticket.rows].tolist()
 
     def choose(self, logits, temperatures=None, seeds=None, counters=None) -> list:
         """One token id per row of float32 ``logits`` [R, V]; waits for the result.

@@ -111,7 +111,7 @@ def test_eos_cancel_arrival_and_failure(models, monkeypatch):
     engine = Engine(model, num_pages=16, page_size=4, max_active=1)
     a, b = engine.submit(prompt, max_new_tokens=3), engine.submit(prompt[:5], max_new_tokens=3, ignore_eos=True)
     real_run = engine.runner.run
-    monkeypatch.setattr(engine.runner, "run", lambda entries: (_ for _ in ()).throw(RuntimeError("injected")))
+    monkeypatch.setattr(engine.runner, "run", lambda *args: (_ for _ in ()).throw(RuntimeError("injected")))
     with pytest.raises(RuntimeError, match="injected"):
         engine.step()
     assert engine.result(a)["state"] == "failed" and engine.result(a)["error"] == "injected"
@@ -124,10 +124,69 @@ def test_eos_cancel_arrival_and_failure(models, monkeypatch):
     engine = Engine(model, num_pages=16, page_size=4)
     c = engine.submit(prompt, max_new_tokens=2)
     monkeypatch.setattr(engine.runner, "run",
-                        lambda entries: torch.full((1, cfg["vocab_size"]), float("nan"), device="cuda"))
+                        lambda *args: torch.full((1, cfg["vocab_size"]), float("nan"), device="cuda"))
     with pytest.raises(RuntimeError, match="non-finite"):
         engine.step()
     assert engine.result(c)["state"] == "failed"
+
+
+def test_running_a_step_ahead_gives_the_same_tokens(models, monkeypatch):
+    """``overlap=True`` queues a step before the host has read the tokens of the step before it (they are fed
+    on the device).  Same requests, same tokens, same reasons to stop as without; events come one call later;
+    a request that stopped on an end-of-sequence token has one more token computed and dropped."""
+    from qwen_inference_lab_b200 import Engine
+    model, weights, cfg = models("B", torch.float32)
+    prompts = [harness.random_tokens(cfg, n, 200 + n) for n in (5, 17, 33, 9, 2)]
+    settings = [dict(max_new_tokens=10), dict(max_new_tokens=7, temperature=0.8, seed=11), dict(max_new_tokens=12),
+                dict(max_new_tokens=1), dict(max_new_tokens=9)]
+    stop_token = plain.greedy(prompts[2], 12, weights, cfg)[4]       # the third request stops on its fifth token
+    def run(overlap):
+        engine = Engine(model, num_pages=40, page_size=8, token_budget=16, prefill_chunk=8, max_active=3,
+                        overlap=overlap)
+        ids, events, calls = [], [], 0
+        for prompt, kw in zip(prompts[:4], settings[:4]):
+            ids.append(engine.submit(prompt, ignore_eos=True, **kw))
+        engine.scheduler.requests[ids[2]].eos = {stop_token}
+        while not engine.idle:
+            got = engine.step()
+            calls += 1
+            if calls == 1:
+                assert bool(got) != overlap or not got      # the first call of a run ahead has nothing to report yet
+            if calls == 3:
+                ids.append(engine.submit(prompts[4], ignore_eos=True, **settings[4]))     # arrives between steps
+            events += [(e["request_id"], e["token_id"], e["finished"]) for e in got]
+        assert engine.cache.free_pages() == 40 and not engine.cache.owners()
+        engine.cache.check_invariants()
+        return [engine.result(i) for i in ids], events, calls
+    plain_rows, plain_events, plain_calls = run(False)
+    ahead_rows, ahead_events, ahead_calls = run(True)
+    for a, b in zip(plain_rows, ahead_rows):
+        assert a["token_ids"] == b["token_ids"] and a["finish_reason"] == b["finish_reason"] and b["state"] == "completed"
+    assert plain_rows[2]["finish_reason"] == "eos" and len(plain_rows[2]["token_ids"]) == 5
+    assert plain_rows[3]["token_ids"] == plain.greedy(prompts[3], 1, weights, cfg)
+    assert sorted(plain_events) == sorted(ahead_events)
+    assert ahead_calls >= plain_calls
+    # cancelling a request whose token is still on the device
+    engine = Engine(model, num_pages=40, page_size=8, overlap=True)
+    a = engine.submit(prompts[1], max_new_tokens=6, ignore_eos=True)
+    engine.step(); engine.step(); engine.step()
+    assert engine.cancel(a)
+    assert engine.step() == [] and engine.idle and engine.cache.free_pages() == 40
+    assert engine.result(a)["state"] == "cancelled"
+    # a step that fails while the one before it is still unread: that one's tokens are kept, the batch is retired
+    engine = Engine(model, num_pages=40, page_size=8, overlap=True, max_active=1)
+    a, b = engine.submit(prompts[0], max_new_tokens=4, ignore_eos=True), engine.submit(prompts[3], max_new_tokens=2, ignore_eos=True)
+    engine.step()
+    real_run = engine.runner.run
+    monkeypatch.setattr(engine.runner, "run", lambda *args: (_ for _ in ()).throw(RuntimeError("injected")))
+    with pytest.raises(RuntimeError, match="injected"):
+        engine.step()
+    monkeypatch.setattr(engine.runner, "run", real_run)
+    assert engine.result(a)["state"] == "failed" and engine.result(a)["token_ids"] == plain.greedy(prompts[0], 1, weights, cfg)
+    while not engine.idle:
+        engine.step()
+    assert engine.result(b)["token_ids"] == plain.greedy(prompts[3], 2, weights, cfg)
+    assert engine.cache.free_pages() == 40
 
 
 def test_bad_submissions_are_rejected_without_allocation(models):

@@ -295,6 +295,20 @@ def test_sample_rows_greedy_ties_and_nonfinite():
     tokens, bad = ops().sample_rows(logits.cuda())
     assert tokens.cpu().tolist()[:2] == [17, 999]
     assert bad.cpu().tolist() == [0, 0, 1, 1]
+    # a vocabulary that is cut into many slices: equal maxima in the first and the last slice, a lone
+    # maximum in the very last entry, a non-finite value in a middle slice; twice, since the slices'
+    # tickets must be back at zero after a call; and more rows than one launch takes
+    wide = torch.randn(4, 100003)
+    wide[0, 123] = 50.0; wide[0, 99990] = 50.0
+    wide[1, 100002] = 60.0
+    wide[2, 51234] = float("-inf")
+    for _ in range(2):
+        tokens, bad = ops().sample_rows(wide.cuda())
+        assert tokens.cpu().tolist()[:2] == [123, 100002] and tokens.cpu().tolist()[3] == int(wide[3].argmax())
+        assert bad.cpu().tolist() == [0, 0, 1, 0]
+    many = torch.randn(5000, 7)
+    tokens, bad = ops().sample_rows(many.cuda())
+    assert torch.equal(tokens.cpu().long(), many.argmax(dim=1)) and int(bad.sum()) == 0
 
 
 def test_sample_rows_temperature_matches_plain_and_is_batch_independent():
