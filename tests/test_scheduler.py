@@ -126,3 +126,30 @@ def test_budgets_must_be_positive_integers():
     for bad in (dict(token_budget=0), dict(prefill_chunk=-1), dict(max_active=1.5)):
         with pytest.raises(ValueError):
             Scheduler(cache, **bad)
+
+
+def test_planning_a_step_ahead_of_the_tokens():
+    """A token that a queued step has sampled and the host has not read counts as input: the next plan feeds
+    its place (marked -1) back, and a request whose pending token is its last gets no further work."""
+    cache, scheduler = make(budget=8, chunk=4)
+    scheduler.add(request(0, 3, new=2)); scheduler.add(request(1, 6, new=3))
+    plan = scheduler.plan()
+    assert [(w.request_id, w.start, w.tokens) for w in plan] == [(0, 0, [1, 2, 3]), (1, 0, [1, 2, 3, 4])]
+    r0, r1 = scheduler.requests[0], scheduler.requests[1]
+    r0.computed, r1.computed = 3, 4
+    r0.pending = 1                              # request 0's first token is on the device
+    assert r0.input_length == 4 and r0.input_slice(2, 2) == [3, -1] and r0.input_slice(3, 1) == [-1]
+    plan = scheduler.plan()                     # request 0 decodes the unread token, request 1 ends its prompt
+    assert [(w.request_id, w.start, w.tokens) for w in plan] == [(0, 3, [-1]), (1, 4, [5, 6])]
+    r0.output.append(55)                        # read now; the step just planned has sampled the second
+    r0.computed, r1.computed, r1.pending = 4, 6, 1
+    assert r0.pending == 1 and r0.ends_with_pending and not r1.ends_with_pending
+    plan = scheduler.plan()                     # request 0 waits for its last token, request 1 goes on
+    assert [(w.request_id, w.start, w.tokens) for w in plan] == [(1, 6, [-1])]
+    r0.output.append(56); r0.pending = 0
+    scheduler.retire(0, "completed", "length")
+    assert list(scheduler.active) == [1]
+    # nothing to plan while the only active request waits for its last token, and no complaint about it
+    r1.output += [7, 8]; r1.computed = 8; r1.pending = 1
+    scheduler.add(request(2, 40, new=20))       # fits the cache, but not beside request 1: waits
+    assert r1.ends_with_pending and scheduler.plan() == [] and list(scheduler.waiting) == [2]
