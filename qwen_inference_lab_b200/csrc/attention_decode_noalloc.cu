@@ -70,7 +70,7 @@ extern "C" int qil_attn_decode_noalloc(const void* q, const void* kv, void* out,
     float* part_o = scratch;
     float* part_ml = scratch + o_floats;
     attn_decode_span_kernel<<<dim3(n_spans, n_kv_heads * chunks, n_decode), 128, smem, stream>>>(
-        p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len);
+        p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len, DecodeTail{});
     {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }

@@ -289,12 +289,105 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     }
 }
 
+// ------------------------------------------------------------------ single tokens: the projection's tail
+// A step of single tokens may hand this kernel the raw output of the query/key/value projection instead
+// of finished queries: every block then norms and rotates the query heads it serves itself, and the
+// block whose span holds the token's own position does the same for that token's key and copies its
+// value, both into the token's cache page, before it reads that tile.  That is the work of the
+// stand-alone kernel in rope_kv.cu, with the same arithmetic and rounding points (per-head RMSNorm with
+// float32 statistics, qil/model.py:52-55; every product and sum of the rotation rounded by itself),
+// without a launch of its own between the projection and the attention.
+struct DecodeTail {
+    const bf16* qkv;          // [N, (Hq + 2 * own_kv_heads) * D]; null: p.q holds finished queries
+    const bf16* q_norm;       // [D] or null
+    const bf16* k_norm;
+    const float* rope;        // [rope_rows][rotary_dim]: cosines then sines; null: no rotation
+    bf16* kv_out;             // the layer's pages, writable
+    float eps;
+    int rotary_dim, rope_rows;
+    int own_kv_heads;         // 0: the layer reads another layer's cache and writes nothing
+};
+
+// One warp: a head of D values from ``src`` through RMSNorm (when ``norm_w``) and the rotation of its
+// first ``rot`` values by the row ``cs`` of the table (when ``cs``), into ``dst`` (shared or global).
+// A lane holds pairs (2 lane + 64 i, +1) of the rotated half, their partners rot / 2 further on, and
+// pairs of the values behind the rotated part.  rot is a multiple of 4.
+__device__ __forceinline__ void warp_norm_rotate_head(const bf16* __restrict__ src, const bf16* __restrict__ norm_w,
+                                                      float eps, const float* __restrict__ cs, int rot,
+                                                      bf16* dst, int lane) {
+    typedef __nv_bfloat162 bf2;
+    constexpr int RUNS = (D / 2 + 63) / 64, REST = (D + 63) / 64;
+    if (cs == nullptr) rot = 0;
+    const int half = rot / 2;
+    const bf2* src2 = reinterpret_cast<const bf2*>(src);
+    bf2 lo[RUNS], hi[RUNS], rest[REST];
+#pragma unroll
+    for (int i = 0; i < RUNS; ++i) {
+        const int j = 2 * lane + 64 * i;
+        if (j < half) { lo[i] = src2[j / 2]; hi[i] = src2[(j + half) / 2]; }
+    }
+#pragma unroll
+    for (int i = 0; i < REST; ++i) {
+        const int j = rot + 2 * lane + 64 * i;
+        if (j < D) rest[i] = src2[j / 2];
+    }
+    if (norm_w != nullptr) {
+        float sq = 0.f;
+#pragma unroll
+        for (int i = 0; i < RUNS; ++i)
+            if (2 * lane + 64 * i < half) {
+                const float2 a = __bfloat1622float2(lo[i]), b = __bfloat1622float2(hi[i]);
+                sq += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+            }
+#pragma unroll
+        for (int i = 0; i < REST; ++i)
+            if (rot + 2 * lane + 64 * i < D) {
+                const float2 a = __bfloat1622float2(rest[i]);
+                sq += a.x * a.x + a.y * a.y;
+            }
+        sq = warp_sum(sq);
+        const float scale = rsqrtf(sq / (float)D + eps);
+        const bf2* w2 = reinterpret_cast<const bf2*>(norm_w);
+        auto normed = [&](bf2 v, int j) {
+            const float2 f = __bfloat1622float2(v);
+            return __hmul2_rn(__floats2bfloat162_rn(f.x * scale, f.y * scale), w2[j / 2]);
+        };
+#pragma unroll
+        for (int i = 0; i < RUNS; ++i) {
+            const int j = 2 * lane + 64 * i;
+            if (j < half) { lo[i] = normed(lo[i], j); hi[i] = normed(hi[i], j + half); }
+        }
+#pragma unroll
+        for (int i = 0; i < REST; ++i) {
+            const int j = rot + 2 * lane + 64 * i;
+            if (j < D) rest[i] = normed(rest[i], j);
+        }
+    }
+    bf2* out2 = reinterpret_cast<bf2*>(dst);
+#pragma unroll
+    for (int i = 0; i < RUNS; ++i) {
+        const int j = 2 * lane + 64 * i;
+        if (j < half) {
+            const float2 cf = *reinterpret_cast<const float2*>(cs + j);
+            const float2 sf = *reinterpret_cast<const float2*>(cs + half + j);
+            const bf2 c = __floats2bfloat162_rn(cf.x, cf.y), sn = __floats2bfloat162_rn(sf.x, sf.y);   // exact: the table is rounded
+            out2[j / 2] = __hsub2_rn(__hmul2_rn(lo[i], c), __hmul2_rn(hi[i], sn));
+            out2[(j + half) / 2] = __hadd2_rn(__hmul2_rn(lo[i], sn), __hmul2_rn(hi[i], c));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < REST; ++i) {
+        const int j = rot + 2 * lane + 64 * i;
+        if (j < D) out2[j / 2] = rest[i];
+    }
+}
+
 // ------------------------------------------------------------------ single tokens: spans
 // decode_info: (token in the flat batch, its absolute position, block-table row, unused) per token.
 // part_o  [n_decode, Hq, n_spans, D] float32, unnormalised; part_ml [n_decode, Hq, n_spans, 2] (max, sum).
 __global__ void __launch_bounds__(128)
 attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int n_spans, int span_len) {
+                        float* __restrict__ part_ml, int n_spans, int span_len, DecodeTail tail) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [16][LDS]
     bf16* sK = sQ + 16 * LDS;                           // [2][64][LDS]
@@ -337,11 +430,42 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     cp_async_commit();
     qil_wait_for_producer();
     qil_release_consumer();
-    {   // the query heads of this kv head: 8 threads per row
+    if (tail.qkv == nullptr) {   // finished queries: the heads of this kv head, 8 threads per row
         const int row = tid >> 3;
         const bool valid = row < gcount;
         const bf16* src = p.q + ((size_t)n * p.n_q_heads + kv_head * group + g0 + (valid ? row : 0)) * D;
         for (int c = tid & 7; c < D / 8; c += 8) cp_async16(sQ + row * LDS + c * 8, src + c * 8, valid);
+    } else {
+        // raw projection: a warp per query head; rows past the group are zero as the copy above leaves them
+        const int total_heads = p.n_q_heads + 2 * tail.own_kv_heads;
+        const bf16* token = tail.qkv + (size_t)n * total_heads * D;
+        const int rope_row = (tail.rope_rows > 0 && pos >= tail.rope_rows) ? tail.rope_rows - 1 : pos;
+        const float* cs = (tail.rope != nullptr && tail.rotary_dim > 0) ? tail.rope + (size_t)rope_row * tail.rotary_dim : nullptr;
+        for (int row = warp; row < 16; row += 4) {
+            if (row < gcount) {
+                warp_norm_rotate_head(token + (size_t)(kv_head * group + g0 + row) * D, tail.q_norm, tail.eps, cs,
+                                      tail.rotary_dim, sQ + row * LDS, lane);
+            } else {
+                for (int c = lane; c < D / 2; c += 32) reinterpret_cast<unsigned*>(sQ + row * LDS)[c] = 0u;
+            }
+        }
+        // The token's own key and value: by the block whose span holds its position, into its page, before
+        // that block (the only one that reads the position) asks for the tile.  The host sends groups of
+        // more than 16 query heads, where several blocks share a kv head's spans, to the stand-alone kernel.
+        if (tail.own_kv_heads > 0 && k_begin <= hi && hi < k_begin + span_len && warp < 2) {
+            const int page = s_pages[hi / p.page_size - first_page];
+            if (page >= 0 && page < p.num_pages) {
+                const size_t slot = (((size_t)page * 2 + warp) * p.n_kv_heads + kv_head) * p.page_size + hi % p.page_size;
+                if (warp == 0)
+                    warp_norm_rotate_head(token + (size_t)(p.n_q_heads + kv_head) * D, tail.k_norm, tail.eps, cs,
+                                          tail.rotary_dim, tail.kv_out + slot * D, lane);
+                else
+                    warp_norm_rotate_head(token + (size_t)(p.n_q_heads + tail.own_kv_heads + kv_head) * D, nullptr, 0.f,
+                                          nullptr, 0, tail.kv_out + slot * D, lane);
+            }
+            __threadfence();      // in L2 before this block's copies of the tile read it
+        }
+        __syncthreads();
     }
     if (!early) issue_kv_tile(p, row_off[0], sK, sV, tid);
     cp_async_commit();
@@ -567,10 +691,11 @@ extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const 
 // decode_info: int32 [n_decode, 4] = (token, its absolute position, block-table row, 0).
 // Scratch: part_o needs n_decode * Hq * n_spans * D floats, part_ml n_decode * Hq * n_spans * 2 floats.
 // n_spans * span_len must cover the longest context of the batch (max position + 1).
-extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
-                               float* part_o, float* part_ml, int n_spans, int span_len,
-                               const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
-                               int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
+static int launch_decode(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
+                         float* part_o, float* part_ml, int n_spans, int span_len,
+                         const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                         int page_size, int num_pages, int window, float scale, const DecodeTail& tail,
+                         cudaStream_t stream) {
     if (n_decode <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
@@ -588,7 +713,7 @@ extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const i
         configured = smem;
     }
     qil_launch_chained(attn_decode_span_kernel, dim3(n_spans, n_kv_heads * chunks, n_decode), dim3(128), smem, stream,
-                       p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len);
+                       p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len, tail);
     {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }
@@ -596,4 +721,41 @@ extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const i
     qil_launch_chained(attn_decode_merge_kernel, dim3(n_q_heads, n_decode), dim3(128), 0, stream,
                        p, (const int4*)decode_info, (const float*)part_o, (const float*)part_ml, n_spans, span_len);
     QIL_CHECK_LAUNCH();
+}
+
+extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
+                               float* part_o, float* part_ml, int n_spans, int span_len,
+                               const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                               int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
+    DecodeTail none = {};
+    return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
+                         table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, none, stream);
+}
+
+// The same over the raw output of the query/key/value projection, for steps in which every token is a single
+// token of its request: qkv [N, (n_q_heads + 2 * own_kv_heads) * D] (queries, keys, values), own_kv_heads
+// either n_kv_heads or 0 (a layer that reads another layer's cache).  The kernel norms and rotates the
+// queries, and norms, rotates and stores each token's key and value into its page of ``kv`` (see DecodeTail).
+// q_norm, k_norm bfloat16 [D] or null; rope float32 [rope_rows, rotary_dim] or null, rotary_dim a multiple
+// of 4.  At most 16 query heads per kv head.
+extern "C" int qil_attn_decode_qkv(const void* qkv, void* kv, void* out, const int* decode_info, int n_decode,
+                                   float* part_o, float* part_ml, int n_spans, int span_len,
+                                   const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                   int own_kv_heads, int page_size, int num_pages, int window, float scale,
+                                   const void* q_norm, const void* k_norm, float eps, const float* rope,
+                                   int rotary_dim, int rope_rows, cudaStream_t stream) {
+    if (qkv == nullptr) QIL_REFUSE("attention: the projection's output is missing");
+    if (n_kv_heads <= 0 || n_q_heads / n_kv_heads > 16)
+        QIL_REFUSE("attention: the fused tail takes at most 16 query heads per kv head");
+    if (own_kv_heads != 0 && own_kv_heads != n_kv_heads) QIL_REFUSE("attention: own_kv_heads is %d or 0", n_kv_heads);
+    if (rope != nullptr && (rotary_dim < 0 || rotary_dim > D || rotary_dim % 4 || rope_rows <= 0))
+        QIL_REFUSE("attention: rotary_dim %d of head size %d, %d table rows", rotary_dim, D, rope_rows);
+    if (((uintptr_t)qkv | (uintptr_t)q_norm | (uintptr_t)k_norm) & 3 || ((uintptr_t)rope & 7))
+        QIL_REFUSE("attention: the projection, norm weights and rotary table must be aligned to 4 and 8 bytes");
+    DecodeTail tail = {};
+    tail.qkv = (const bf16*)qkv; tail.q_norm = (const bf16*)q_norm; tail.k_norm = (const bf16*)k_norm;
+    tail.rope = rope; tail.kv_out = (bf16*)kv; tail.eps = eps; tail.rotary_dim = rope ? rotary_dim : 0;
+    tail.rope_rows = rope_rows; tail.own_kv_heads = own_kv_heads;
+    return launch_decode(qkv, kv, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
+                         table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, tail, stream);
 }

@@ -104,6 +104,43 @@ def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_
         "attention (single tokens)", kernels=2)
 
 
+def projection_tail_usable(ctx, qkv, cache, n_q_heads, n_kv_heads, head_dim, rotary_dim, norm_weights) -> bool:
+    """Can the single-token kernel take the projection's raw output (``attend_projection``)?  Every token of
+    the step a single token of its request, bfloat16 throughout, at most 16 query heads per kv head."""
+    return (ctx.n_decode == ctx.n_tokens and ctx.n_tiles == 0 and qkv.dtype == torch.bfloat16
+            and cache.pages.dtype == torch.bfloat16 and supports(head_dim, n_q_heads, n_kv_heads)
+            and n_q_heads // n_kv_heads <= 16 and rotary_dim % 4 == 0 and rotary_dim <= head_dim
+            and all(w is None or w.dtype == torch.bfloat16 for w in norm_weights))
+
+
+def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads, head_dim, window, scale,
+                      q_norm, k_norm, eps, rope_table, rotary_dim):
+    """A step of single tokens, straight from the q/k/v projection: ``qkv`` bfloat16
+    [N, (n_q_heads + 2 * own_kv_heads) * D].  The kernel norms and rotates the queries itself and writes
+    each token's normed, rotated key and its value into the token's page before reading them, so the
+    norm/rotation/store kernel is not launched.  ``own_kv_heads``: n_kv_heads, or 0 for a layer that
+    reads another layer's cache."""
+    if tuple(cache.pages.shape[1:]) != (2, n_kv_heads, cache.page_size, head_dim):
+        raise KernelError(f"attention: cache layout {tuple(cache.pages.shape)}")
+    if qkv.shape != (ctx.n_tokens, (n_q_heads + 2 * own_kv_heads) * head_dim) or not qkv.is_contiguous():
+        raise KernelError(f"attention: projection output {tuple(qkv.shape)}")
+    if rope_table is not None and (rope_table.dtype != torch.float32 or rope_table.shape[1] != rotary_dim
+                                   or not rope_table.is_contiguous()):
+        raise KernelError("attention: the rotary table must be float32 [positions, rotary_dim]")
+    span_len = choose_span(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim)
+    n_spans = max(1, (ctx.max_context + span_len - 1) // span_len)
+    part_o, part_ml = decode_scratch(ctx, ctx.n_decode, n_q_heads, n_spans, head_dim)
+    lib = library(head_dim)
+    _check(lib, lib.qil_attn_decode_qkv(
+        _p(qkv), _p(cache.pages), _p(out), _p(ctx.decode_info), c_int(ctx.n_decode), _p(part_o), _p(part_ml),
+        c_int(n_spans), c_int(span_len), _p(cache.block_table), c_int(cache.block_table.shape[1]),
+        c_int(n_q_heads), c_int(n_kv_heads), c_int(own_kv_heads), c_int(cache.page_size),
+        c_int(cache.pages.shape[0]), c_int(window), c_float(scale), _p(q_norm), _p(k_norm), c_float(float(eps)),
+        _p(rope_table), c_int(rotary_dim if rope_table is not None else 0),
+        c_int(rope_table.shape[0] if rope_table is not None else 0), _stream()),
+        "attention (single tokens from the projection)", kernels=2)
+
+
 def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
     """q, out bfloat16 [N, Hq*D]; cache a KVCacheView whose pages already hold this step's keys and values."""
     if q.dtype != torch.bfloat16 or cache.pages.dtype != torch.bfloat16:

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import gemm_tc, ops
+from ..kernels import attention_mma, gemm_tc, ops
 from .base import KVCacheSpec, Mixer, Param
 from .linear import Linear, StackedLinear
 
@@ -78,7 +78,6 @@ class GroupedQueryAttention(Mixer):
         the block's un-normed input and the first projection applies the norm."""
         n = x.shape[0]
         n_kv = 0 if self.reads_shared_cache else self.n_kv_heads
-        q = ctx.empty((n, self.n_q_heads * self.head_dim))
         table = self.position.table if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         q_norm = self.q_norm.data if self.q_norm is not None else None
@@ -87,6 +86,7 @@ class GroupedQueryAttention(Mixer):
             # long prompt portions: one tcgen05 kernel projects, norms, rotates and writes the pages
             if norm is not None:
                 x = norm.forward(ctx, x)
+            q = ctx.empty((n, self.n_q_heads * self.head_dim))
             gemm_tc.gemm_tc_qkv(x, self.qkv._weight(), self.qkv._bias(), q, cache.pages, table, q_norm, k_norm,
                                 self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, ctx.positions,
                                 ctx.token_row, cache.block_table, self.n_q_heads, n_kv, cache.page_size)
@@ -94,18 +94,23 @@ class GroupedQueryAttention(Mixer):
             self._attend(ctx, q, cache, attended)
             return self.out.forward(ctx, attended, residual=residual)
         qkv = self.qkv.forward(ctx, x, norm=norm)
-        ops.qk_norm_rope_store(
-            qkv, q, cache.pages, self.q_norm.data if self.q_norm is not None else None,
-            self.k_norm.data if self.k_norm is not None else None,
-            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, table, rotary_dim,
-            ctx.positions, ctx.token_row, cache.block_table, self.n_q_heads, n_kv, self.head_dim,
-            cache.page_size)
+        eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
+        if attention_mma.projection_tail_usable(ctx, qkv, cache, self.n_q_heads, self.n_kv_heads, self.head_dim,
+                                                rotary_dim, (q_norm, k_norm)):
+            # a step of single tokens: the attention kernel norms, rotates and stores what it needs itself
+            attended = ctx.empty((n, self.n_q_heads * self.head_dim))
+            attention_mma.attend_projection(ctx, qkv, cache, attended, self.n_q_heads, self.n_kv_heads, n_kv,
+                                            self.head_dim, self.window, self.scale, q_norm, k_norm, eps, table,
+                                            rotary_dim)
+            return self.out.forward(ctx, attended, residual=residual)
+        q = ctx.empty((n, self.n_q_heads * self.head_dim))
+        ops.qk_norm_rope_store(qkv, q, cache.pages, q_norm, k_norm, eps, table, rotary_dim, ctx.positions,
+                               ctx.token_row, cache.block_table, self.n_q_heads, n_kv, self.head_dim, cache.page_size)
         attended = ctx.empty((n, self.n_q_heads * self.head_dim))
         self._attend(ctx, q, cache, attended)
         return self.out.forward(ctx, attended, residual=residual)
 
     def _attend(self, ctx, q, cache, out):
-        from ..kernels import attention_mma
         if q.dtype == torch.bfloat16 and attention_mma.supports(self.head_dim, self.n_q_heads, self.n_kv_heads):
             attention_mma.attend(ctx, q, cache, out, self.n_q_heads, self.n_kv_heads, self.head_dim,
                                  self.window, self.scale)

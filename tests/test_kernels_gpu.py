@@ -269,6 +269,61 @@ def test_span_choice_fills_the_gpu_and_stays_legal():
     assert attention_mma.choose_span(8, 32, 8, 8192) in (640, 1408)
 
 
+@pytest.mark.parametrize("n_q,n_kv,d,lengths,page,window,rotary,norms,own", [
+    (32, 8, 128, [2100, 64, 641], 16, 0, 128, True, True),
+    (6, 3, 80, [520, 130, 1], 16, 64, 40, True, True),        # half of the head rotated, a window, a first token
+    (4, 1, 48, [300, 77], 8, 0, 0, False, True),              # no rotation, no norms
+    (16, 2, 64, [257, 70], 4, 0, 64, True, False),            # a layer that reads another layer's cache
+])
+def test_attention_single_tokens_from_the_projection(n_q, n_kv, d, lengths, page, window, rotary, norms, own):
+    """The single-token kernel fed with the raw q/k/v projection (it norms, rotates and stores what it needs)
+    against the two kernels it replaces: the same outputs and the same pages, bit for bit."""
+    from types import SimpleNamespace
+    from qwen_inference_lab_b200.kernels import attention_mma
+    from qwen_inference_lab_b200.parts.rotary import rotary_table
+    _, pool, table, meta, _ = attention_case(n_q, n_kv, d, lengths, [n - 1 for n in lengths], torch.bfloat16, page,
+                                             seed=16, window=window)
+    torch.manual_seed(17)
+    n, own_kv, eps = len(lengths), (n_kv if own else 0), 1e-5
+    qkv = torch.randn(n, (n_q + 2 * own_kv) * d).to(torch.bfloat16).cuda()
+    q_norm = (1 + 0.3 * torch.randn(d)).to(torch.bfloat16).cuda() if norms else None
+    k_norm = (1 + 0.3 * torch.randn(d)).to(torch.bfloat16).cuda() if norms else None
+    rope = rotary_table(rotary, 10000.0, 4096, torch.bfloat16).cuda() if rotary else None
+    as_int = lambda values: torch.tensor(values, dtype=torch.int32).cuda()
+    positions, token_row = as_int([m - 1 for m in lengths]), as_int(meta["seg_row"])
+    decode_info = as_int([v for i in range(n) for v in (i, lengths[i] - 1, meta["seg_row"][i], 0)])
+    longest = max(lengths)
+    for span_len in (64, 256, 2048):
+        n_spans = (longest + span_len - 1) // span_len
+        scratch = lambda: (torch.full((n * n_q * n_spans * d,), float("nan")).cuda(),
+                           torch.full((n * n_q * n_spans * 2,), float("nan")).cuda())
+        # the two kernels
+        pages_a = pool.cuda().clone()
+        q = torch.empty(n, n_q * d, dtype=torch.bfloat16).cuda()
+        ops().qk_norm_rope_store(qkv, q, pages_a, q_norm, k_norm, eps, rope, rotary, positions, token_row, table.cuda(),
+                                 n_q, own_kv, d, page)
+        out_a = torch.full((n, n_q * d), float("nan"), dtype=torch.bfloat16).cuda()
+        attention_mma.decode(q, pages_a, out_a, decode_info, n, *scratch(), n_spans, span_len, table.cuda(), n_q, n_kv,
+                             d, page, window, d ** -0.5)
+        # the one kernel
+        pages_b = pool.cuda().clone()
+        out_b = torch.full((n, n_q * d), float("nan"), dtype=torch.bfloat16).cuda()
+        part_o, part_ml = scratch()
+        ctx = SimpleNamespace(n_tokens=n, n_decode=n, n_tiles=0, max_context=n_spans * span_len, decode_info=decode_info,
+                              extras={"attn_decode_scratch": (part_o, part_ml)}, device=qkv.device)
+        cache = SimpleNamespace(pages=pages_b, block_table=table.cuda(), page_size=page)
+        assert attention_mma.projection_tail_usable(ctx, qkv, cache, n_q, n_kv, d, rotary, (q_norm, k_norm))
+        import unittest.mock
+        with unittest.mock.patch.object(attention_mma, "choose_span", lambda *a, **k: span_len):
+            attention_mma.attend_projection(ctx, qkv, cache, out_b, n_q, n_kv, own_kv, d, window, d ** -0.5, q_norm,
+                                            k_norm, eps, rope, rotary)
+        torch.cuda.synchronize()
+        assert not torch.isnan(out_b).any()
+        assert torch.equal(out_a, out_b)
+        same = (pages_a == pages_b) | (torch.isnan(pages_a) & torch.isnan(pages_b))
+        assert bool(same.all())
+
+
 @pytest.mark.parametrize("form", ["portion", "single"])
 def test_attention_far_key_stands_out(form):
     """One key hundreds of positions back dominates the softmax: dropping it would change everything."""
