@@ -85,6 +85,8 @@ struct AttnParams {
     int table_stride;
     int n_q_heads, n_kv_heads, page_size, num_pages, window;
     float scale_log2;         // head_dim^-1/2 * log2(e)
+    int slots;                // single tokens: blocks of the span kernel that the GPU runs at a time
+    int blocks_per_span;      // single tokens: blocks that share a span index (tokens x kv heads x head chunks)
 };
 
 // Where the key row of position ``pos`` of one kv head starts, in units of 16 bytes from the layer's
@@ -289,6 +291,30 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     }
 }
 
+// ------------------------------------------------------------------ single tokens: how long a span
+// When the caller leaves the span length to the kernels (span_len 0), both kernels of the pair derive it
+// from the step's longest context (the fourth int of every decode_info entry) with a small cost model:
+// blocks run in waves of `slots`; a wave takes about (tiles per span + 2) tile times, the 2 standing for a
+// block's start-up; every further span costs a little in the merge.  The grid's span count is the cap.
+// A recorded graph can so be replayed while contexts grow, with the span that suits each step.
+// Every warp evaluates the candidates itself, one per lane (2048 / 64 = 32 candidates), and takes the
+// cheapest, the shortest among equals: a few dozen instructions, no shared memory, no barrier.
+static_assert(MAX_DECODE_SPAN / KV_TILE == 32, "one candidate span length per lane");
+__device__ __forceinline__ int pick_span_len(int max_context, int n_spans_cap, int blocks_per_span, int slots) {
+    const int tiles = max(1, (max_context + KV_TILE - 1) / KV_TILE);
+    const int span_tiles = (threadIdx.x & 31) + 1;
+    const int n_spans = (tiles + span_tiles - 1) / span_tiles;
+    const int waves = (blocks_per_span * n_spans + slots - 1) / slots;
+    // in units of 1/20 tile time, as integers: comparisons are exact and the same in both kernels
+    const long long cost = 20ll * waves * (span_tiles + 2) + 3ll * n_spans;
+    const int key = (n_spans <= n_spans_cap && cost < (1 << 24)) ? (int)cost * 64 + span_tiles : 0x7fffffff;
+    // cost first, then the shorter span
+    int best = key;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+    return (best == 0x7fffffff ? MAX_DECODE_SPAN / KV_TILE : (best & 63)) * KV_TILE;
+}
+
 // ------------------------------------------------------------------ single tokens: the projection's tail
 // A step of single tokens may hand this kernel the raw output of the query/key/value projection instead
 // of finished queries: every block then norms and rotates the query heads it serves itself, and the
@@ -387,7 +413,7 @@ __device__ __forceinline__ void warp_norm_rotate_head(const bf16* __restrict__ s
 // part_o  [n_decode, Hq, n_spans, D] float32, unnormalised; part_ml [n_decode, Hq, n_spans, 2] (max, sum).
 __global__ void __launch_bounds__(128)
 attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int n_spans, int span_len, DecodeTail tail) {
+                        float* __restrict__ part_ml, int n_spans, int span_len_arg, DecodeTail tail) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [16][LDS]
     bf16* sK = sQ + 16 * LDS;                           // [2][64][LDS]
@@ -405,6 +431,7 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     const int n = info.x, pos = info.y;
     const int hi = pos;
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int span_len = span_len_arg > 0 ? span_len_arg : pick_span_len(info.w, n_spans, p.blocks_per_span, p.slots);
     const int k_begin = span * span_len;
     if (k_begin > hi || k_begin + span_len <= lo) return;    // the merge skips the same spans
     const int* table = p.block_table + (size_t)info.z * p.table_stride;
@@ -595,13 +622,14 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
 // ------------------------------------------------------------------ single tokens: merge of the spans
 __global__ void __launch_bounds__(128)
 attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, const float* __restrict__ part_o,
-                         const float* __restrict__ part_ml, int n_spans, int span_len) {
+                         const float* __restrict__ part_ml, int n_spans, int span_len_arg) {
     qil_wait_for_producer();
     qil_release_consumer();
     const int head = blockIdx.x, d_idx = blockIdx.y;
     const int4 info = decode_info[d_idx];
     const int n = info.x, pos = info.y;
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int span_len = span_len_arg > 0 ? span_len_arg : pick_span_len(info.w, n_spans, p.blocks_per_span, p.slots);
     const int s_lo = lo / span_len;
     int s_hi = pos / span_len;
     if (s_hi >= n_spans) s_hi = n_spans - 1;   // cannot happen when the host sized n_spans for the batch
@@ -647,6 +675,8 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.slots = 1;
+    p.blocks_per_span = 1;
     return 0;
 }
 
@@ -658,7 +688,7 @@ static int decode_smem_bytes(int span_len, int page_size) {
 }
 
 static int check_decode_span(int span_len, int n_spans) {
-    if (span_len < KV_TILE || span_len > MAX_DECODE_SPAN || span_len % KV_TILE)
+    if (span_len != 0 && (span_len < KV_TILE || span_len > MAX_DECODE_SPAN || span_len % KV_TILE))
         QIL_REFUSE("attention: a span of %d positions; spans are multiples of %d up to %d", span_len, KV_TILE, MAX_DECODE_SPAN);
     if (n_spans <= 0) QIL_REFUSE("attention: n_spans %d", n_spans);
     return 0;
@@ -690,7 +720,9 @@ extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const 
 
 // decode_info: int32 [n_decode, 4] = (token, its absolute position, block-table row, 0).
 // Scratch: part_o needs n_decode * Hq * n_spans * D floats, part_ml n_decode * Hq * n_spans * 2 floats.
-// n_spans * span_len must cover the longest context of the batch (max position + 1).
+// n_spans * span_len must cover the longest context of the batch (max position + 1).  span_len 0 leaves the
+// span length to the kernels: the fourth int of every decode_info entry must then hold the step's longest
+// context, and n_spans * 2048 must cover it; n_spans caps the number of spans used.
 static int launch_decode(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
                          float* part_o, float* part_ml, int n_spans, int span_len,
                          const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
@@ -705,13 +737,26 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention: decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
     if (n_kv_heads * chunks > 65535 || n_decode > 65535) QIL_REFUSE("attention: grid too large");
-    const int smem = decode_smem_bytes(span_len, page_size);
+    const int smem = decode_smem_bytes(span_len > 0 ? span_len : MAX_DECODE_SPAN, page_size);
     static int configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_span_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = smem;
     }
+    static int sm_count = 0, per_sm = 0;
+    if (sm_count == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
+            sm_count = 148;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_span_kernel, 128, smem) != cudaSuccess || per_sm <= 0) {
+            (void)cudaGetLastError();
+            per_sm = 1;
+        }
+    }
+    p.slots = sm_count * per_sm;
+    p.blocks_per_span = n_decode * n_kv_heads * chunks;
     qil_launch_chained(attn_decode_span_kernel, dim3(n_spans, n_kv_heads * chunks, n_decode), dim3(128), smem, stream,
                        p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len, tail);
     {

@@ -119,10 +119,12 @@ class StepRunner:
         for name in ("positions", "seg_pos0"):
             begin = offsets[name][0]
             packed[begin:begin + n] = starts
+        longest = int(starts.max()) + 1
         begin = offsets["decode_info"][0]
         packed[begin + 1:begin + 4 * n:4] = starts
+        packed[begin + 3:begin + 4 * n:4] = longest
         host = dict(host, seg_pos0=starts)
-        return packed, offsets, host, n, n, int(starts.max()) + 1
+        return packed, offsets, host, n, n, longest
 
     def _describe(self, entries):
         """Host arrays of the batch, packed into one int32 vector with section offsets."""
@@ -160,9 +162,10 @@ class StepRunner:
         rest.sort(key=lambda t: -(t[1] + t[2]))
         big_tile_info = np.array(big, dtype=np.int64).reshape(-1)
         rest_tile_info = np.array(rest, dtype=np.int64).reshape(-1)
-        # single-token segments: (token, its position, block-table row, 0)
+        # single-token segments: (token, its position, block-table row, the longest context among them)
         single = np.nonzero(lens == 1)[0]
-        decode_info = np.stack([seg_start[single], starts[single], rows[single], np.zeros_like(single)],
+        decode_info = np.stack([seg_start[single], starts[single], rows[single],
+                                np.full_like(single, int(starts[single].max()) + 1)],
                                axis=1).reshape(-1) if len(single) else np.zeros(0, dtype=np.int64)
         # places of tokens that are still on the device: (index in the flat batch, index in the source buffer)
         feed = np.array([v for i, e in enumerate(entries) if e.feed is not None

@@ -38,6 +38,16 @@ def library(head_dim):
 _sm_count = None
 
 
+def _slots(head_dim) -> int:
+    """Blocks of the span kernel that run at a time: SMs x blocks per SM (shared memory decides)."""
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count \
+            if torch.cuda.is_available() else 148
+    block_smem = (16 + 4 * KV_TILE) * (head_dim + 8) * 2 + 2048
+    return _sm_count * max(1, min(3, (227 * 1024) // block_smem))
+
+
 def choose_span(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> int:
     """Positions per block of the single-token kernel, from a small cost model.
 
@@ -45,15 +55,12 @@ def choose_span(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> i
     times, the 2 standing for a block's start-up (its metadata, page ids and first tile arrive one
     after the other); every further span also costs a little in the merge.  The span with the
     lowest cost wins; measured on B200 at context 8192 this picks 1408 for batch 8 (384 blocks, one
-    wave: 54 us against 58-66 us for spans of 384 to 1024) and 1664 for batch 64.
+    wave: 54 us against 58-66 us for spans of 384 to 1024) and 1664 for batch 64.  The kernels hold the
+    same model (``pick_span_len``) and use it when they are given a span length of 0, with the step's
+    own longest context; this function serves callers that fix the span themselves.
     """
-    global _sm_count
-    if _sm_count is None:
-        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count \
-            if torch.cuda.is_available() else 148
     blocks_per_span = n_decode * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16)
-    block_smem = (16 + 4 * KV_TILE) * (head_dim + 8) * 2 + 2048
-    slots = _sm_count * max(1, min(3, (227 * 1024) // block_smem))
+    slots = _slots(head_dim)
     tiles = max(1, (max_context + KV_TILE - 1) // KV_TILE)
     best, best_cost = 1, None
     for span_tiles in range(1, MAX_DECODE_SPAN // KV_TILE + 1):
@@ -63,6 +70,17 @@ def choose_span(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> i
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = span_tiles, cost
     return best * KV_TILE
+
+
+def span_cap(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> int:
+    """The most spans the kernels may use for any context up to ``max_context`` when they choose the
+    span length themselves (the grid's first dimension, and what the scratch is sized for).  The cost
+    model never prefers a second wave of shorter spans to one wave, so one wave's worth of spans is
+    enough unless the longest span (2048 positions) forces more."""
+    slots, blocks_per_span = _slots(head_dim), n_decode * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16)
+    tiles = max(1, (max_context + KV_TILE - 1) // KV_TILE)
+    longest = MAX_DECODE_SPAN // KV_TILE
+    return min(tiles, max(-(-slots // blocks_per_span), -(-tiles // longest)) + 1)
 
 
 def decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim):
@@ -127,8 +145,9 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
     if rope_table is not None and (rope_table.dtype != torch.float32 or rope_table.shape[1] != rotary_dim
                                    or not rope_table.is_contiguous()):
         raise KernelError("attention: the rotary table must be float32 [positions, rotary_dim]")
-    span_len = choose_span(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim)
-    n_spans = max(1, (ctx.max_context + span_len - 1) // span_len)
+    # the kernels pick the span from the step's own longest context (decode_info carries it); ctx.max_context
+    # may be a recorded graph's upper bound and only caps the number of spans
+    span_len, n_spans = 0, span_cap(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim)
     part_o, part_ml = decode_scratch(ctx, ctx.n_decode, n_q_heads, n_spans, head_dim)
     lib = library(head_dim)
     _check(lib, lib.qil_attn_decode_qkv(
@@ -158,8 +177,7 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
         prefill(q, cache.pages, out, ctx.tile_info, ctx.n_tiles, cache.block_table, n_q_heads, n_kv_heads,
                 head_dim, cache.page_size, window, scale)
     if ctx.n_decode:
-        span_len = choose_span(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim)
-        n_spans = max(1, (ctx.max_context + span_len - 1) // span_len)
+        span_len, n_spans = 0, span_cap(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim)
         part_o, part_ml = decode_scratch(ctx, ctx.n_decode, n_q_heads, n_spans, head_dim)
         decode(q, cache.pages, out, ctx.decode_info, ctx.n_decode, part_o, part_ml, n_spans, span_len,
                cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale)

@@ -152,7 +152,8 @@ class StepContext:
     # 4 ints each = (first token in the flat batch, its absolute position, rows in the tile, block-table row)
     n_tiles: int
     tile_info: torch.Tensor          # [n_tiles * 4]
-    # segments of exactly one token (decode rows): 4 ints each = (token, its position, block-table row, 0)
+    # segments of exactly one token (decode rows): 4 ints each = (token, its position, block-table row,
+    # the longest context among these segments)
     n_decode: int
     decode_info: torch.Tensor        # [n_decode * 4]
     max_context: int                 # largest start+len over the batch's segments (host upper bound)
