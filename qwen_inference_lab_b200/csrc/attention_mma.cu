@@ -306,7 +306,13 @@ __device__ __forceinline__ int pick_span_len(int max_context, int n_spans_cap, i
     const int n_spans = (tiles + span_tiles - 1) / span_tiles;
     const int waves = (blocks_per_span * n_spans + slots - 1) / slots;
     // in units of 1/20 tile time, as integers: comparisons are exact and the same in both kernels
-    const long long cost = 20ll * waves * (span_tiles + 2) + 3ll * n_spans;
+#ifndef SPAN_STARTUP20
+#define SPAN_STARTUP20 40     // a block's start-up in 1/20 tile times
+#endif
+#ifndef SPAN_MERGE20
+#define SPAN_MERGE20 3        // what one more span costs the merge, in 1/20 tile times
+#endif
+    const long long cost = (long long)waves * (20 * span_tiles + SPAN_STARTUP20) + (long long)SPAN_MERGE20 * n_spans;
     const int key = (n_spans <= n_spans_cap && cost < (1 << 24)) ? (int)cost * 64 + span_tiles : 0x7fffffff;
     // cost first, then the shorter span
     int best = key;
