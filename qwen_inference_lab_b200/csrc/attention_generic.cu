@@ -53,7 +53,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
         const bool valid = key >= lo && key <= pos;
         long long off = -1;
         if (valid) {
-            const int page = table[key / page_size];
+            const int page = key / page_size < table_stride ? table[key / page_size] : -1;
             if (page >= 0 && page < num_pages)
                 off = ((((long long)page * 2) * n_kv_heads + kv_head) * page_size + (key % page_size)) * head_dim;
         }

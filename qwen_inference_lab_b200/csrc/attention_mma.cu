@@ -94,7 +94,7 @@ struct AttnParams {
 // [lo, hi] or holds no page.  ``pages`` holds the request's page ids from logical page ``first_page`` on.
 __device__ __forceinline__ int kv_row_offset(const AttnParams& p, const int* pages, int first_page, int kv_head,
                                              int pos, int lo, int hi) {
-    if (pos < lo || pos > hi) return -1;
+    if (pos < lo || pos > hi || pos / p.page_size >= p.table_stride) return -1;
     const int page = pages[pos / p.page_size - first_page];
     if (page < 0 || page >= p.num_pages) return -1;
     return (int)((((size_t)page * 2 * p.n_kv_heads + kv_head) * p.page_size + (pos % p.page_size)) * (D / 8));
@@ -447,7 +447,8 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     // the page ids of the whole span, once: a tile's loads then wait for no table read
     const int first_page = (first_tile * KV_TILE) / p.page_size;
     const int last_page = min((last_tile + 1) * KV_TILE - 1, hi) / p.page_size;
-    for (int i = tid; i <= last_page - first_page; i += 128) s_pages[i] = table[first_page + i];
+    for (int i = tid; i <= last_page - first_page; i += 128)
+        s_pages[i] = first_page + i < p.table_stride ? table[first_page + i] : -1;
     __syncthreads();
     __shared__ int row_off[2][KV_TILE];
     if (tid < KV_TILE) {

@@ -235,7 +235,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int j = 0; j < n_tiles; ++j) {
             if (j % tiles_per_batch == 0) {
                 const int index = j * pages_per_tile + lane;
-                my_page = index <= last_page ? table[index] : -1;
+                my_page = (index <= last_page && index < p.table_stride) ? table[index] : -1;
             }
             const int stage = j % AT_STAGES;
             const unsigned parity = ((j / AT_STAGES) & 1) ^ 1;

@@ -202,7 +202,8 @@ __device__ __forceinline__ void tc_store_qkv_head(unsigned taddr, int m, int M, 
         dst = t.q_out + ((size_t)m * t.n_q_heads + head) * 128;
     } else {
         const int kv_head = is_k ? head - t.n_q_heads : head - t.n_q_heads - t.n_kv_heads;
-        const int page = t.block_table[(size_t)t.token_row[m] * t.table_stride + pos / t.page_size];
+        const int index = pos / t.page_size;                 // a position the table has no entry for writes nothing
+        const int page = (pos >= 0 && index < t.table_stride) ? t.block_table[(size_t)t.token_row[m] * t.table_stride + index] : -1;
         if (page < 0 || page >= t.num_pages) return;        // never write outside the pool
         dst = t.pages + ((((size_t)page * 2 + (is_k ? 0 : 1)) * t.n_kv_heads + kv_head) * t.page_size + pos % t.page_size) * 128;
     }

@@ -56,7 +56,8 @@ __global__ void qk_norm_rope_store_kernel(
         dst = q_out + ((size_t)token * n_q_heads + head) * head_dim;
     } else {
         const int kv_head = is_k ? head - n_q_heads : head - n_q_heads - n_kv_heads;
-        const int page = block_table[(size_t)token_row[token] * table_stride + pos / page_size];
+        const int index = pos / page_size;       // a position the table has no entry for writes nothing
+        const int page = (pos >= 0 && index < table_stride) ? block_table[(size_t)token_row[token] * table_stride + index] : -1;
         if (page < 0 || page >= num_pages) return;  // host validation failed; never write outside the pool
         dst = kv_cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * n_kv_heads + kv_head) * page_size
                           + (pos % page_size)) * head_dim;
@@ -111,7 +112,8 @@ qk_norm_rope_store_bf16_kernel(
     const int total_heads = n_q_heads + 2 * n_kv_heads;
     // the token's position and page first: their latency hides behind the first head's loads
     int pos = positions[token];
-    const int page = (n_kv_heads > 0) ? block_table[(size_t)token_row[token] * table_stride + pos / page_size] : 0;
+    const int page = (n_kv_heads > 0) ? ((pos >= 0 && pos / page_size < table_stride)
+        ? block_table[(size_t)token_row[token] * table_stride + pos / page_size] : -1) : 0;
     const int slot = page_size > 0 ? pos % page_size : 0;
     if (pos >= table_rows && table_rows > 0) pos = table_rows - 1;
     constexpr int RUNS = HD ? (HD / 2 + 63) / 64 : ROPE_FAST_MAX_D / 2 / 64;   // runs of 64 elements in a rotated half
