@@ -108,13 +108,27 @@ rmsnorm_bf16x8_kernel(const bf16* __restrict__ x, const W* __restrict__ weight, 
     for (int i = 0; i < RMS_VPT; ++i) {
         const int idx = threadIdx.x + i * 256;
         if (idx >= vectors) continue;
-        const bf16* e = reinterpret_cast<const bf16*>(&v[i]);
         uint4 o4;
-        bf16* o = reinterpret_cast<bf16*>(&o4);
+        if (sizeof(W) == 2) {
+            // bfloat16 weights: one 16-byte read, and the product of the rounded value and the weight as a
+            // packed bfloat16 multiply (one rounding, never contracted with anything)
+            const uint4 w4 = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(weight) + idx * 8);
+            const __nv_bfloat162* e2 = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&w4);
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const float normed = round_to<bf16>(__bfloat162float(e[k]) * scale);
-            o[k] = __float2bfloat16_rn(normed * to_f32<W>(weight[idx * 8 + k]));
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(e2[k]);
+                o2[k] = __hmul2_rn(__floats2bfloat162_rn(f.x * scale, f.y * scale), w2[k]);
+            }
+        } else {
+            const bf16* e = reinterpret_cast<const bf16*>(&v[i]);
+            bf16* o = reinterpret_cast<bf16*>(&o4);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float normed = round_to<bf16>(__bfloat162float(e[k]) * scale);
+                o[k] = __float2bfloat16_rn(normed * to_f32<W>(weight[idx * 8 + k]));
+            }
         }
         dst[idx] = o4;
     }
@@ -126,7 +140,7 @@ extern "C" int qil_rmsnorm(const void* x, const void* weight, const int* rows, v
     if (n_rows <= 0) return 0;
     if (width <= 0) QIL_REFUSE("rmsnorm: width %d", width);
     if (act_dtype == QIL_BF16 && width % 8 == 0 && width <= 256 * 8 * RMS_VPT &&
-        (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        (((uintptr_t)x | (uintptr_t)out | (uintptr_t)weight) & 15) == 0) {
         if (weight_dtype == QIL_BF16)
             qil_launch_chained(rmsnorm_bf16x8_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream,
                                (const bf16*)x, (const bf16*)weight, rows, (bf16*)out, width, eps);
