@@ -630,8 +630,7 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
 __global__ void __launch_bounds__(128)
 attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, const float* __restrict__ part_o,
                          const float* __restrict__ part_ml, int n_spans, int span_len_arg) {
-    qil_wait_for_producer();
-    qil_release_consumer();
+    // the step's description is older than the kernel before this one: read it while that one finishes
     const int head = blockIdx.x, d_idx = blockIdx.y;
     const int4 info = decode_info[d_idx];
     const int n = info.x, pos = info.y;
@@ -641,6 +640,8 @@ attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, con
     int s_hi = pos / span_len;
     if (s_hi >= n_spans) s_hi = n_spans - 1;   // cannot happen when the host sized n_spans for the batch
     const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
+    qil_wait_for_producer();
+    qil_release_consumer();
     // every thread reads the few (max, sum) pairs itself: the loads are independent and overlap
     float mx = -INFINITY;
     for (int s = s_lo; s <= s_hi; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
@@ -649,7 +650,7 @@ attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, con
     float acc[(D + 127) / 128];
 #pragma unroll
     for (int i = 0; i < (D + 127) / 128; ++i) acc[i] = 0.f;
-#pragma unroll 4
+#pragma unroll 8
     for (int s = s_lo; s <= s_hi; ++s) {
         const float f = exp2f(part_ml[(base + s) * 2] - ms);
         sum += f * part_ml[(base + s) * 2 + 1];
