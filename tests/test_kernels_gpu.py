@@ -372,6 +372,28 @@ def test_sample_rows_greedy_ties_and_nonfinite():
     assert torch.equal(tokens.cpu().long(), many.argmax(dim=1)) and int(bad.sum()) == 0
 
 
+def test_feed_tokens_and_the_sampler_tickets():
+    """Tokens that stay on the device between two steps: the kernel that puts them into the next step's
+    token list (out-of-range places and sources are left alone), and the sampler's begin/finish pair."""
+    from qwen_inference_lab_b200.sampling import NonFiniteLogits, Sampler
+    token_ids = torch.tensor([5, -1, 7, -1, -1, 9], dtype=torch.int32).cuda()
+    pairs = torch.tensor([1, 2, 3, 0, 4, 99, 77, 1], dtype=torch.int32).cuda()      # (place, source) pairs
+    source = torch.tensor([40, 41, 42], dtype=torch.int32).cuda()
+    ops().feed_tokens(token_ids, pairs, 4, source)
+    assert token_ids.cpu().tolist() == [5, 42, 7, 40, -1, 9]
+    sampler = Sampler("cuda", max_rows=2)
+    logits = torch.randn(3, 1000)
+    first = sampler.begin(logits.cuda())
+    second = sampler.begin((-logits).cuda())              # two tickets may be open at a time
+    assert sampler.finish(first) == logits.argmax(dim=1).tolist()
+    assert first.tokens.cpu().tolist() == logits.argmax(dim=1).tolist()
+    assert sampler.finish(second) == logits.argmin(dim=1).tolist()
+    bad = logits.clone(); bad[1, 3] = float("nan")
+    with pytest.raises(NonFiniteLogits):
+        sampler.finish(sampler.begin(bad.cuda()))
+    assert sampler.choose(logits.cuda()) == logits.argmax(dim=1).tolist()
+
+
 def test_sample_rows_temperature_matches_plain_and_is_batch_independent():
     torch.manual_seed(8)
     vocab = 1517
