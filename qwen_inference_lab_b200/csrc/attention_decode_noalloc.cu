@@ -53,7 +53,6 @@ extern "C" int qil_attn_decode_noalloc(const void* q, const void* kv, void* out,
     if (check_decode_span(span_len, n_spans)) return -1;
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention (no allocation): decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
-    if (n_kv_heads * chunks > 65535 || n_decode > 65535) QIL_REFUSE("attention (no allocation): grid too large");
     const long long slots = (long long)n_decode * n_q_heads * n_spans;
     const long long o_floats = (slots * D + 63) / 64 * 64;          // part_ml starts on a 256-byte boundary
     const long long needed = o_floats + (slots * 2 + 63) / 64 * 64;
@@ -61,6 +60,7 @@ extern "C" int qil_attn_decode_noalloc(const void* q, const void* kv, void* out,
         QIL_REFUSE("attention (no allocation): %d tokens x %d heads x %d spans need %lld floats of scratch, "
                    "the built-in array holds %lld; use qil_attn_decode with your own buffers",
                    n_decode, n_q_heads, n_spans, needed, (long long)QIL_NOALLOC_MAX_FLOATS);
+    if (n_decode > 65535 || n_spans > 65535) QIL_REFUSE("attention (no allocation): grid too large");
     // the largest shared memory any legal span can ask for, so that one set-up serves every later call
     const int smem_limit = decode_smem_bytes(MAX_DECODE_SPAN, 1);
     const int smem = decode_smem_bytes(span_len, page_size);
@@ -69,7 +69,7 @@ extern "C" int qil_attn_decode_noalloc(const void* q, const void* kv, void* out,
     if (status != 0) return status;
     float* part_o = scratch;
     float* part_ml = scratch + o_floats;
-    attn_decode_span_kernel<<<dim3(n_spans, n_kv_heads * chunks, n_decode), 128, smem, stream>>>(
+    attn_decode_span_kernel<<<dim3(n_kv_heads * chunks, n_decode, n_spans), 128, smem, stream>>>(
         p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len, DecodeTail{});
     {
         cudaError_t e = cudaGetLastError();

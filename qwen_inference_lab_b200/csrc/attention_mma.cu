@@ -299,20 +299,31 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
 // A recorded graph can so be replayed while contexts grow, with the span that suits each step.
 // Every warp evaluates the candidates itself, one per lane (2048 / 64 = 32 candidates), and takes the
 // cheapest, the shortest among equals: a few dozen instructions, no shared memory, no barrier.
+//
+// The spans of a context are equal but for the last, which takes what is left and is shorter.  Blocks
+// are numbered span by span (the span index is the grid's slowest dimension), so the short last spans
+// start last: a few blocks more than the GPU runs at a time cost nothing if they are short spans that
+// find a slot as soon as the first short spans are done (`2 * (last + start-up)` below).
 static_assert(MAX_DECODE_SPAN / KV_TILE == 32, "one candidate span length per lane");
-__device__ __forceinline__ int pick_span_len(int max_context, int n_spans_cap, int blocks_per_span, int slots) {
-    const int tiles = max(1, (max_context + KV_TILE - 1) / KV_TILE);
-    const int span_tiles = (threadIdx.x & 31) + 1;
-    const int n_spans = (tiles + span_tiles - 1) / span_tiles;
-    const int waves = (blocks_per_span * n_spans + slots - 1) / slots;
-    // in units of 1/20 tile time, as integers: comparisons are exact and the same in both kernels
 #ifndef SPAN_STARTUP20
 #define SPAN_STARTUP20 40     // a block's start-up in 1/20 tile times
 #endif
 #ifndef SPAN_MERGE20
 #define SPAN_MERGE20 3        // what one more span costs the merge, in 1/20 tile times
 #endif
-    const long long cost = (long long)waves * (20 * span_tiles + SPAN_STARTUP20) + (long long)SPAN_MERGE20 * n_spans;
+__device__ __forceinline__ int pick_span_len(int max_context, int n_spans_cap, int blocks_per_span, int slots) {
+    const int tiles = max(1, (max_context + KV_TILE - 1) / KV_TILE);
+    const int span_tiles = (threadIdx.x & 31) + 1;
+    const int n_spans = (tiles + span_tiles - 1) / span_tiles;
+    const int last_tiles = tiles - (n_spans - 1) * span_tiles;
+    const long long whole = (long long)blocks_per_span * (n_spans - 1), all = whole + blocks_per_span;
+    const long long one = 20ll * span_tiles + SPAN_STARTUP20;
+    long long time;
+    if (all <= slots) time = one;
+    else if (blocks_per_span + 2 * whole <= 2ll * slots) time = max(one, 2 * (20ll * last_tiles + SPAN_STARTUP20));
+    else time = (all + slots - 1) / slots * one;
+    // in units of 1/20 tile time, as integers: comparisons are exact and the same in both kernels
+    const long long cost = time + (long long)SPAN_MERGE20 * n_spans;
     const int key = (n_spans <= n_spans_cap && cost < (1 << 24)) ? (int)cost * 64 + span_tiles : 0x7fffffff;
     // cost first, then the shorter span
     int best = key;
@@ -430,9 +441,9 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = p.n_q_heads / p.n_kv_heads;
     const int chunks = (group + 15) / 16;
-    const int kv_head = blockIdx.y / chunks, g0 = (blockIdx.y % chunks) * 16;
+    const int kv_head = blockIdx.x / chunks, g0 = (blockIdx.x % chunks) * 16;
     const int gcount = min(16, group - g0);
-    const int span = blockIdx.x, d_idx = blockIdx.z;
+    const int span = blockIdx.z, d_idx = blockIdx.y;     // the span index varies slowest: see pick_span_len
     const int4 info = decode_info[d_idx];
     const int n = info.x, pos = info.y;
     const int hi = pos;
@@ -744,7 +755,7 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
     if (part_o == nullptr || part_ml == nullptr) QIL_REFUSE("attention: decode needs scratch for %d spans", n_spans);
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention: decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
-    if (n_kv_heads * chunks > 65535 || n_decode > 65535) QIL_REFUSE("attention: grid too large");
+    if (n_decode > 65535 || n_spans > 65535) QIL_REFUSE("attention: grid too large");
     const int smem = decode_smem_bytes(span_len > 0 ? span_len : MAX_DECODE_SPAN, page_size);
     static int configured = 0;
     if (smem > configured) {
@@ -765,7 +776,7 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
     }
     p.slots = sm_count * per_sm;
     p.blocks_per_span = n_decode * n_kv_heads * chunks;
-    qil_launch_chained(attn_decode_span_kernel, dim3(n_spans, n_kv_heads * chunks, n_decode), dim3(128), smem, stream,
+    qil_launch_chained(attn_decode_span_kernel, dim3(n_kv_heads * chunks, n_decode, n_spans), dim3(128), smem, stream,
                        p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len, tail);
     {
         cudaError_t e = cudaGetLastError();
