@@ -461,17 +461,37 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     for (int i = tid; i <= last_page - first_page; i += 128)
         s_pages[i] = first_page + i < p.table_stride ? table[first_page + i] : -1;
     __syncthreads();
-    __shared__ int row_off[2][KV_TILE];
-    if (tid < KV_TILE) {
-        row_off[0][tid] = kv_row_offset(p, s_pages, first_page, kv_head, first_tile * KV_TILE + tid, lo, hi);
-        row_off[1][tid] = kv_row_offset(p, s_pages, first_page, kv_head, (first_tile + 1) * KV_TILE + tid, lo,
-                                        min(hi, (last_tile + 1) * KV_TILE - 1));
-    }
-    __syncthreads();
+    // From here to the merge at the end the four warps run on their own.  A warp owns 16 keys of every
+    // 64-key tile: it copies exactly those rows of K and V into its part of the two tile buffers, needs
+    // only warp-level barriers around them, and asks for the rows of tile t + 2 as soon as it is done
+    // with the rows of tile t (K after the scores, V after the output), so two tiles are in flight per
+    // warp instead of one per block.  cp.async groups of a thread, in order: K0, V0, K1, V1, K2, ...
+    constexpr int CPR = D / 8;                   // 16-byte pieces per row
+    const size_t v_plane = (size_t)p.n_kv_heads * p.page_size * D;
+    auto row_offset = [&](int tile) {            // lanes 0..15: where this warp's row `lane` of the tile starts
+        return (lane < 16 && tile <= last_tile)
+            ? kv_row_offset(p, s_pages, first_page, kv_head, tile * KV_TILE + warp * 16 + lane, lo, hi) : -1;
+    };
+    auto issue_rows = [&](int offset_of_lane, bf16* dst, size_t plane) {
+#pragma unroll
+        for (int i = 0; i < 16 * CPR / 32; ++i) {
+            const int idx = i * 32 + lane;
+            const int row = idx / CPR, piece = idx % CPR;
+            const int off = __shfl_sync(0xffffffffu, offset_of_lane, row);
+            const bool valid = off >= 0;
+            cp_async16(dst + row * LDS + piece * 8, p.kv + (size_t)(valid ? off : 0) * 8 + piece * 8 + (valid ? plane : 0), valid);
+        }
+    };
+    bf16* const my_k = sK + warp * 16 * LDS;    // this warp's rows of buffer 0; buffer 1 lies KV_TILE rows further
+    bf16* const my_v = sV + warp * 16 * LDS;
+    constexpr int BUFFER = KV_TILE * LDS;
+    const int off0 = row_offset(first_tile), off1 = row_offset(first_tile + 1);
     // The first tile starts before the wait unless it holds this step's own position, whose key and
-    // value the kernel before this one is still writing.
+    // value are written below (or by the kernel before this one).
     const bool early = first_tile != hi / KV_TILE;
-    if (early) issue_kv_tile(p, row_off[0], sK, sV, tid);
+    if (early) issue_rows(off0, my_k, 0);
+    cp_async_commit();
+    if (early) issue_rows(off0, my_v, v_plane);
     cp_async_commit();
     qil_wait_for_producer();
     qil_release_consumer();
@@ -512,8 +532,13 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
         }
         __syncthreads();
     }
-    if (!early) issue_kv_tile(p, row_off[0], sK, sV, tid);
+    if (!early) { issue_rows(off0, my_k, 0); issue_rows(off0, my_v, v_plane); }
+    if (first_tile + 1 <= last_tile) issue_rows(off1, my_k + BUFFER, 0);
     cp_async_commit();
+    if (first_tile + 1 <= last_tile) issue_rows(off1, my_v + BUFFER, v_plane);
+    cp_async_commit();
+    cp_async_wait<1>();          // the queries and the first tiles' keys; only the second tile's values may be under way
+    __syncthreads();             // the query rows are every warp's
 
     unsigned qf[Q_IN_REGS ? KSTEPS : 1][4];
     float o[D / 8][4];
@@ -523,21 +548,17 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
 
     for (int tile = first_tile; tile <= last_tile; ++tile) {
         const int buf = (tile - first_tile) & 1;
-        if (tile + 1 <= last_tile)
-            issue_kv_tile(p, row_off[buf ^ 1], sK + (buf ^ 1) * KV_TILE * LDS, sV + (buf ^ 1) * KV_TILE * LDS, tid);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        if (tile + 2 <= last_tile && tid < KV_TILE)
-            row_off[buf][tid] = kv_row_offset(p, s_pages, first_page, kv_head, (tile + 2) * KV_TILE + tid, lo, hi);
+        const int off2 = row_offset(tile + 2);
+        cp_async_wait<3>();          // this tile's keys: at most V(t), K(t+1), V(t+1) may still be under way
+        __syncwarp();
         if (Q_IN_REGS && tile == first_tile) {
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks)
                 ldmatrix_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
                             sQ + (((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + ks * 16 + (lane >> 4) * 8);
         }
-        const bf16* tK = sK + buf * KV_TILE * LDS + warp * 16 * LDS;   // this warp's 16 keys of the tile
-        const bf16* tV = sV + buf * KV_TILE * LDS + warp * 16 * LDS;
+        const bf16* tK = my_k + buf * BUFFER;   // this warp's 16 keys of the tile
+        const bf16* tV = my_v + buf * BUFFER;
         float s[2][4];
         s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
         s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
@@ -555,6 +576,9 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
             mma_bf16(s[0], a, b0, b1);
             mma_bf16(s[1], a, b2, b3);
         }
+        __syncwarp();                // every lane has read the keys: their rows take tile t + 2
+        if (tile + 2 <= last_tile) issue_rows(off2, my_k + buf * BUFFER, 0);
+        cp_async_commit();
         float tmax = -INFINITY;     // every row is the same position: one mask for all
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
@@ -590,6 +614,8 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
         a[1] = pack_bf16(s[0][2], s[0][3]);
         a[2] = pack_bf16(s[1][0], s[1][1]);
         a[3] = pack_bf16(s[1][2], s[1][3]);
+        cp_async_wait<3>();          // this tile's values: K(t+1), V(t+1), K(t+2) may still be under way
+        __syncwarp();
 #pragma unroll
         for (int dp = 0; dp < D / 16; ++dp) {
             unsigned b0, b1, b2, b3;
@@ -597,9 +623,12 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
             mma_bf16(o[2 * dp], a, b0, b1);
             mma_bf16(o[2 * dp + 1], a, b2, b3);
         }
-        __syncthreads();
+        __syncwarp();
+        if (tile + 2 <= last_tile) issue_rows(off2, my_v + buf * BUFFER, v_plane);
+        cp_async_commit();
     }
     cp_async_wait<0>();
+    __syncthreads();             // every warp is done with its rows: the buffers become the merge's scratch
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
 
