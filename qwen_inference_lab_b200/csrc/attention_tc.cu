@@ -12,7 +12,8 @@
 //               buffers in tensor memory, and O += P V once the softmax warps have published P;
 //               it runs one score tile ahead of the softmax;
 //   warps 2-5   one thread per query row: tcgen05.ld of its 128 scores, mask, running maximum, exp2,
-//               row sum, P as bfloat16 into shared memory in the operand layout of the second MMA,
+//               row sum, P as bfloat16 back into tensor memory over the scores it came from (the
+//               second MMA takes its first operand from there: no shared memory, no proxy fence),
 //               and the rescale of O in tensor memory when the running maximum moved by more than
 //               2^8 (until then P is computed against the older maximum, which is exact algebra and
 //               safe in float32); finally O / l -> global memory.
@@ -35,7 +36,6 @@ QIL_ERROR_STORAGE
 #define AT_QTILE (2 * AT_QSLAB)  // the query tile: two halves of the head
 #define AT_SLAB (AT_N * 128)     // bytes of a [keys][64 elements] slab of K or V
 #define AT_TILE (2 * AT_SLAB)    // a K or V tile: two halves of the head
-#define AT_PTILE ((AT_N / 64) * AT_QSLAB)   // P: [128 rows][keys], one slab per 64 keys
 #define AT_TMEM_COLS (AT_N == 64 ? 256 : 512)
 #define AT_STAGES 2
 #define AT_WAIT_CYCLES 2000000000ll
@@ -101,6 +101,15 @@ __device__ __forceinline__ void at_mma(unsigned tmem_d, unsigned long long da, u
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
                  ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
 }
+// The same with the first operand in tensor memory (lane = row, two 16-bit elements per 32-bit column,
+// the reduction dimension along the columns).
+__device__ __forceinline__ void at_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long db, unsigned idesc, unsigned acc) {
+    const unsigned zero = 0u;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(acc), "r"(zero) : "memory");
+}
 __device__ __forceinline__ void at_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(at_smem(bar)) : "memory");
 }
@@ -148,7 +157,7 @@ struct AtShared {
     unsigned long long q_full;
     unsigned long long k_full[AT_STAGES], k_empty[AT_STAGES];
     unsigned long long v_full[AT_STAGES], v_empty[AT_STAGES];
-    unsigned long long s_full[2], s_empty[2];
+    unsigned long long s_full[2];
     unsigned long long p_full, pv_done;
     unsigned tmem_base;
     unsigned pad;
@@ -178,8 +187,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     unsigned char* sQ = base;                               // [2 slabs]
     unsigned char* sK = sQ + AT_QTILE;                      // [stages][2 slabs]
     unsigned char* sV = sK + AT_STAGES * AT_TILE;           // [stages][2 slabs]
-    unsigned char* sP = sV + AT_STAGES * AT_TILE;           // [keys / 64 slabs]: keys 0..63, 64..127
-    AtShared* sh = reinterpret_cast<AtShared*>(sP + AT_PTILE);
+    AtShared* sh = reinterpret_cast<AtShared*>(sV + AT_STAGES * AT_TILE);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heads vary fastest, so all heads of the longest tile start first (tiles come sorted, longest first)
     const int head = blockIdx.x;
@@ -197,7 +205,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             at_mbar_init(&sh->k_full[s], 1); at_mbar_init(&sh->k_empty[s], 1);
             at_mbar_init(&sh->v_full[s], 1); at_mbar_init(&sh->v_empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) { at_mbar_init(&sh->s_full[b], 1); at_mbar_init(&sh->s_empty[b], 4); }
+        for (int b = 0; b < 2; ++b) at_mbar_init(&sh->s_full[b], 1);
         at_mbar_init(&sh->p_full, 4);
         at_mbar_init(&sh->pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -289,7 +297,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             auto issue_scores = [&](int j) -> bool {
                 const int stage = j % AT_STAGES, buf = j & 1;
                 if (!at_wait(&sh->k_full[stage], (j / AT_STAGES) & 1)) { atomicExch(p.error_word, 14); return false; }
-                if (!at_wait(&sh->s_empty[buf], ((j >> 1) & 1) ^ 1)) { atomicExch(p.error_word, 15); return false; }
+                // The score buffer of tile j held P of tile j - 2: the MMA that read it was issued before this one
+                // and MMAs run in the order of their issue, so the buffer needs no barrier of its own.
                 at_fence_after();
                 const unsigned q_addr = at_smem(sQ), k_addr = at_smem(sK + stage * AT_TILE);
 #pragma unroll
@@ -312,13 +321,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (!at_wait(&sh->p_full, j & 1)) { atomicExch(p.error_word, 17); ok = false; break; }
                 AT_STAMP(1, 4 * j + 2);
                 at_fence_after();
-                const unsigned p_addr = at_smem(sP), v_addr = at_smem(sV + stage * AT_TILE);
+                const unsigned v_addr = at_smem(sV + stage * AT_TILE);
 #pragma unroll
                 for (int kk = 0; kk < AT_N / 16; ++kk) {
-                    // P: 16 keys = 32 bytes inside the key half; V: 16 keys = 16 rows of 128 bytes
-                    const unsigned p_off = (kk >> 2) * AT_QSLAB + (kk & 3) * 32;
-                    at_mma(tmem_o, at_desc_kmajor(p_addr + p_off), at_desc_mnmajor(v_addr + kk * 2048), idesc_pv,
-                           (j | kk) ? 1u : 0u);
+                    // P: 16 keys = 8 columns of tensor memory; V: 16 keys = 16 rows of 128 bytes
+                    at_mma_ts(tmem_o, tmem_s[j & 1] + kk * 8, at_desc_mnmajor(v_addr + kk * 2048), idesc_pv,
+                              (j | kk) ? 1u : 0u);
                 }
                 at_commit(&sh->pv_done);
                 at_commit(&sh->v_empty[stage]);
@@ -349,9 +357,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[c][i]);
             }
-            at_fence_before();
-            __syncwarp();
-            if (lane == 0) at_arrive(&sh->s_empty[buf]);      // the score buffer may be overwritten
             if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j + 2);
             // scale, mask by absolute position (only tiles that reach past the first row's position need it)
             const int key0 = j * AT_N;
@@ -416,16 +421,19 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     }
                 }
             }
-            // P into the K-major operand image: row `row`, 16-byte chunk c of each 128-byte half-row goes to
-            // chunk (c ^ (row & 7))
-            unsigned char* p_row = sP + row * 128;
+            // P over the scores it came from: this thread's row, two keys per 32-bit column
+            {
+                unsigned words[AT_N / 2];
 #pragma unroll
-            for (int c = 0; c < AT_N / 8; ++c) {
-                const int half = c >> 3, chunk = c & 7;
-                *reinterpret_cast<uint4*>(p_row + half * AT_QSLAB + ((chunk ^ (row & 7)) << 4)) = packed[c];
+                for (int c = 0; c < AT_N / 8; ++c) {
+                    words[4 * c] = packed[c].x; words[4 * c + 1] = packed[c].y;
+                    words[4 * c + 2] = packed[c].z; words[4 * c + 3] = packed[c].w;
+                }
+                static_assert(AT_N == 64, "one 32-column store per row");
+                at_tmem_st32(tmem_s[buf] + lane_base, words);
+                at_wait_st();
             }
-            // make the shared-memory writes visible to the tensor core's reads, and order the TMEM stores
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            if (j == n_tiles - 1) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the zeroed value rows
             at_fence_before();
             __syncwarp();
             if (lane == 0) at_arrive(&sh->p_full);
@@ -527,7 +535,7 @@ extern "C" int qil_attn_tc_prefill(const void* q, const void* kv, void* out, con
     p.scale_log2 = scale * 1.4426950408889634f;
     p.error_word = error_word;
     p.trace = trace;
-    const int smem = AT_QTILE + 2 * AT_STAGES * AT_TILE + AT_PTILE + (int)sizeof(AtShared);
+    const int smem = AT_QTILE + 2 * AT_STAGES * AT_TILE + (int)sizeof(AtShared);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
