@@ -5,9 +5,9 @@
 // qil/model.py:59-68); this kernel takes the bulk of long prompt portions, the mma.sync kernel what
 // is left over.
 //
-// One block per (tile of 128 query tokens, query head), 192 threads:
-//   warp 0      one thread issues TMA loads: the query tile once, then per 128 keys the pages of K
-//               and of V (one box per page and 64-wide half of the head, 128-byte swizzle);
+// One block per (tile of 128 query tokens, query head), 224 threads:
+//   warp 0, 6   issue TMA loads: warp 0 the query tile once and then per 64 keys the pages of K, warp 6 the
+//               pages of V (one box per page and 64-wide half of the head, 128-byte swizzle);
 //   warp 1      one thread issues tcgen05.mma: S = Q K^T (128 x 128 x 128) into one of two score
 //               buffers in tensor memory, and O += P V once the softmax warps have published P;
 //               it runs one score tile ahead of the softmax;
@@ -158,7 +158,7 @@ struct AtShared {
     unsigned long long k_full[AT_STAGES], k_empty[AT_STAGES];
     unsigned long long v_full[AT_STAGES], v_empty[AT_STAGES];
     unsigned long long s_full[2];
-    unsigned long long p_full, pv_done;
+    unsigned long long p_full[2], pv_done;
     unsigned tmem_base;
     unsigned pad;
 };
@@ -173,7 +173,9 @@ struct AtParams {
     long long* trace;           // only read when compiled with AT_TRACE
 };
 
-__global__ void __launch_bounds__(192, (AT_N == 64) ? 2 : 1)
+#define AT_VALUE_WARP 6                  // warps: 0 keys, 1 MMA issue, 2-5 softmax, 6 values
+#define AT_THREADS 224
+__global__ void __launch_bounds__(AT_THREADS, (AT_N == 64) ? 2 : 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                AtParams p, const int4* __restrict__ tile_info) {
     // swizzled operand tiles need 1024-byte alignment; the declaration asks for it and a misaligned
@@ -206,7 +208,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             at_mbar_init(&sh->v_full[s], 1); at_mbar_init(&sh->v_empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) at_mbar_init(&sh->s_full[b], 1);
-        at_mbar_init(&sh->p_full, 4);
+        at_mbar_init(&sh->p_full[0], 4);
+        at_mbar_init(&sh->p_full[1], 4);
         at_mbar_init(&sh->pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -219,21 +222,31 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     __syncthreads();
     at_fence_after();
     const unsigned tmem = sh->tmem_base;
-    const unsigned tmem_s[2] = {tmem, tmem + (unsigned)AT_N};
+    auto tmem_s = [tmem](int buffer) { return tmem + (unsigned)(buffer * AT_N); };    // the two score buffers
     const unsigned tmem_o = tmem + 2u * AT_N;
 
-    if (warp == 0) {
-        // The whole warp walks the tiles: every lane fetches one block-table entry of a batch of 32 in one
-        // coalesced read, lane 0 waits, arms the barriers and issues the copies with ids handed over by
-        // shuffles (a dependent table read per page would cost the producer more than a tile's MMAs).
+    if (warp == 0 || warp == AT_VALUE_WARP) {
+        // Two producer warps, one for the keys (and the queries) and one for the values: a stage of keys is
+        // free as soon as the scores of two tiles ago are computed, a stage of values only when that tile's
+        // output is, and the next scores must not wait behind a copy of values.  The whole warp walks the
+        // tiles: every lane fetches one block-table entry of a batch of 32 in one coalesced read, lane 0
+        // waits and arms the barrier, and the copies go out one per lane (lane = half of the head, page of
+        // the tile) with page ids handed over by shuffles; issuing a tile's copies from one thread one after
+        // the other would cost that thread more than the tile's MMAs take.
+        const int kv = warp == 0 ? 0 : 1;
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_q) : "memory");
             asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_kv) : "memory");
-            // queries: box (64 elements, 1 head, 128 tokens) per half of the head
-            at_expect_tx(&sh->q_full, AT_QTILE);
-            at_tma_3d(sQ, &map_q, &sh->q_full, 0, head, n0);
-            at_tma_3d(sQ + AT_QSLAB, &map_q, &sh->q_full, 64, head, n0);
+            if (kv == 0) {
+                asm volatile("prefetch.tensormap [%0];\n" ::"l"((unsigned long long)&map_q) : "memory");
+                // queries: box (64 elements, 1 head, 128 tokens) per half of the head
+                at_expect_tx(&sh->q_full, AT_QTILE);
+                at_tma_3d(sQ, &map_q, &sh->q_full, 0, head, n0);
+                at_tma_3d(sQ + AT_QSLAB, &map_q, &sh->q_full, 64, head, n0);
+            }
         }
+        unsigned long long* const full = kv == 0 ? sh->k_full : sh->v_full;
+        unsigned long long* const empty = kv == 0 ? sh->k_empty : sh->v_empty;
+        unsigned char* const tiles = kv == 0 ? sK : sV;
         const int pages_per_tile = AT_N / p.page_size;
         const int tiles_per_batch = 32 / pages_per_tile;       // pages_per_tile is 1, 2, 4 or 8
         const int page_bytes = p.page_size * 128;               // one page of one half: page_size rows of 128 bytes
@@ -250,38 +263,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const int first_key = j * AT_N;
             int pages = pages_per_tile;
             if (first_key + AT_N - 1 > hi) pages = (hi - first_key) / p.page_size + 1;
-            // one copy per lane: lane = (half of the head, page of the tile).  Keys first: their stage is free
-            // as soon as the scores of two tiles ago are computed, long before the values' stage, and the
-            // next scores need them first.  (Issuing a tile's copies from one thread one after the other
-            // costs that thread more than the tile's MMAs take.)
             const int pg = lane % pages_per_tile, half = (lane / pages_per_tile) & 1;
             const int page = __shfl_sync(0xffffffffu, my_page, (j % tiles_per_batch) * pages_per_tile + pg);
-            for (int kv = 0; kv < 2; ++kv) {
-                if (lane == 0 && ok) {
-                    if (!at_wait(kv == 0 ? &sh->k_empty[stage] : &sh->v_empty[stage], parity)) {
-                        atomicExch(p.error_word, 11);
-                        ok = 0;
-                    } else {
-                        at_expect_tx(kv == 0 ? &sh->k_full[stage] : &sh->v_full[stage], (unsigned)(pages * 2 * page_bytes));
-                    }
+            if (lane == 0) {
+                if (!at_wait(&empty[stage], parity)) {
+                    atomicExch(p.error_word, 11);
+                    ok = 0;
+                } else {
+                    at_expect_tx(&full[stage], (unsigned)(pages * 2 * page_bytes));
                 }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (ok && lane < 2 * pages_per_tile && pg < pages) {
-                    // cache rows of one layer: ((page * 2 + kv) * kv_heads + kv_head) * page_size + slot
-                    const int row = ((page * 2 + kv) * p.n_kv_heads + kv_head) * p.page_size;
-                    unsigned char* dst = (kv == 0 ? sK : sV) + stage * AT_TILE + half * AT_SLAB + pg * page_bytes;
-                    at_tma_2d(dst, &map_kv, kv == 0 ? &sh->k_full[stage] : &sh->v_full[stage], half * 64, row);
-                }
-                if (lane == 0) AT_STAMP(0, 2 * j + kv);
             }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
+            if (lane < 2 * pages_per_tile && pg < pages) {
+                // cache rows of one layer: ((page * 2 + kv) * kv_heads + kv_head) * page_size + slot
+                const int row = ((page * 2 + kv) * p.n_kv_heads + kv_head) * p.page_size;
+                at_tma_2d(tiles + stage * AT_TILE + half * AT_SLAB + pg * page_bytes, &map_kv, &full[stage], half * 64, row);
+            }
+            if (lane == 0) AT_STAMP(0, 2 * j + kv);
         }
         // leave only after the copies have been consumed or have had a second to land
         if (lane == 0 && ok) {
             for (int j = n_tiles; j < n_tiles + AT_STAGES; ++j) {
-                const int stage = j % AT_STAGES;
-                const unsigned parity = ((j / AT_STAGES) & 1) ^ 1;
-                if (!at_wait(&sh->k_empty[stage], parity) || !at_wait(&sh->v_empty[stage], parity)) {
+                if (!at_wait(&empty[j % AT_STAGES], ((j / AT_STAGES) & 1) ^ 1)) {
                     atomicExch(p.error_word, 12);
                     break;
                 }
@@ -304,7 +308,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
                 for (int kk = 0; kk < AT_D / 16; ++kk) {
                     // half of the head, then 16 elements = 32 bytes inside the 128-byte row
-                    at_mma(tmem_s[buf], at_desc_kmajor(q_addr + (kk >> 2) * AT_QSLAB + (kk & 3) * 32),
+                    at_mma(tmem_s(buf), at_desc_kmajor(q_addr + (kk >> 2) * AT_QSLAB + (kk & 3) * 32),
                            at_desc_kmajor(k_addr + (kk >> 2) * AT_SLAB + (kk & 3) * 32), idesc_s, kk ? 1u : 0u);
                 }
                 at_commit(&sh->s_full[buf]);
@@ -318,14 +322,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 const int stage = j % AT_STAGES;
                 if (!at_wait(&sh->v_full[stage], (j / AT_STAGES) & 1)) { atomicExch(p.error_word, 16); ok = false; break; }
                 AT_STAMP(1, 4 * j + 1);
-                if (!at_wait(&sh->p_full, j & 1)) { atomicExch(p.error_word, 17); ok = false; break; }
+                // one barrier per score buffer: the softmax may publish P of the next tile before this thread has
+                // looked at this tile's barrier (nothing holds it back but the scores, which are issued above),
+                // and a single barrier would then be two phases on, which a parity cannot tell from none
+                if (!at_wait(&sh->p_full[j & 1], (j >> 1) & 1)) { atomicExch(p.error_word, 17); ok = false; break; }
                 AT_STAMP(1, 4 * j + 2);
                 at_fence_after();
                 const unsigned v_addr = at_smem(sV + stage * AT_TILE);
 #pragma unroll
                 for (int kk = 0; kk < AT_N / 16; ++kk) {
                     // P: 16 keys = 8 columns of tensor memory; V: 16 keys = 16 rows of 128 bytes
-                    at_mma_ts(tmem_o, tmem_s[j & 1] + kk * 8, at_desc_mnmajor(v_addr + kk * 2048), idesc_pv,
+                    at_mma_ts(tmem_o, tmem_s(j & 1) + kk * 8, at_desc_mnmajor(v_addr + kk * 2048), idesc_pv,
                               (j | kk) ? 1u : 0u);
                 }
                 at_commit(&sh->pv_done);
@@ -333,7 +340,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 AT_STAMP(1, 4 * j + 3);
             }
         }
-    } else {
+    } else if (warp < AT_VALUE_WARP) {
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;                 // query row of this thread = its TMEM lane
         const int pos = pos0 + row;
@@ -350,7 +357,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             {
                 unsigned r[AT_N / 32][32];
 #pragma unroll
-                for (int c = 0; c < AT_N / 32; ++c) at_tmem_ld32(tmem_s[buf] + lane_base + c * 32, r[c]);
+                for (int c = 0; c < AT_N / 32; ++c) at_tmem_ld32(tmem_s(buf) + lane_base + c * 32, r[c]);
                 at_wait_ld();                                  // one wait for all the loads
 #pragma unroll
                 for (int c = 0; c < AT_N / 32; ++c)
@@ -358,44 +365,52 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[c][i]);
             }
             if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j + 2);
-            // scale, mask by absolute position (only tiles that reach past the first row's position need it)
+            // Mask by absolute position (only tiles that reach past the first row's position need it) and take
+            // the row's maximum of the raw scores; the scale (positive) is applied to the maximum and, fused
+            // with the subtraction, inside the exponent.  Four running maxima and four running sums: one
+            // chain of 64 dependent operations would cost this warp, alone on its scheduler, their latency.
             const int key0 = j * AT_N;
-            float tmax = -INFINITY;
-            if (key0 + AT_N - 1 <= pos0) {
+            if (key0 + AT_N - 1 > pos0) {
 #pragma unroll
-                for (int i = 0; i < AT_N; ++i) { s[i] *= p.scale_log2; tmax = fmaxf(tmax, s[i]); }
-            } else {
-#pragma unroll
-                for (int i = 0; i < AT_N; ++i) {
-                    s[i] = (key0 + i <= pos) ? s[i] * p.scale_log2 : -INFINITY;
-                    tmax = fmaxf(tmax, s[i]);
-                }
+                for (int i = 0; i < AT_N; ++i) s[i] = (key0 + i <= pos) ? s[i] : -INFINITY;
             }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < AT_N; i += 4) {
+                mx[0] = fmaxf(mx[0], s[i]); mx[1] = fmaxf(mx[1], s[i + 1]);
+                mx[2] = fmaxf(mx[2], s[i + 2]); mx[3] = fmaxf(mx[3], s[i + 3]);
+            }
+            const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
             // Move the maximum only when it grew by more than 2^8: until then exp2(s - m_used) <= 256,
             // harmless in float32 and bfloat16, and O needs no rescale (which costs a TMEM round trip).
             const bool grow = tmax > m_used + 8.0f;            // also true at the first tile (m_used = -inf)
             const float factor = (grow && j > 0) ? at_exp2(m_used - tmax) : 1.0f;
             if (grow) m_used = tmax;
-            const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-            // P = exp2(s - m) as bfloat16, kept in registers until the buffer is free
-            float sum = 0.f;
+            const float minus_m = (m_used == -INFINITY) ? 0.f : -m_used;
+            // P = exp2(s * scale - m) as bfloat16, kept in registers until it is stored
+            float sums[4] = {0.f, 0.f, 0.f, 0.f};
             uint4 packed[AT_N / 8];
 #pragma unroll
             for (int c = 0; c < AT_N / 8; ++c) {
                 float e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { e[i] = at_exp2(s[c * 8 + i] - m_safe); sum += e[i]; }
+                for (int i = 0; i < 8; ++i) {
+                    e[i] = at_exp2(fmaf(s[c * 8 + i], p.scale_log2, minus_m));
+                    sums[i & 3] += e[i];
+                }
                 __nv_bfloat162 b0 = __floats2bfloat162_rn(e[0], e[1]), b1 = __floats2bfloat162_rn(e[2], e[3]);
                 __nv_bfloat162 b2 = __floats2bfloat162_rn(e[4], e[5]), b3 = __floats2bfloat162_rn(e[6], e[7]);
                 packed[c].x = *reinterpret_cast<unsigned*>(&b0); packed[c].y = *reinterpret_cast<unsigned*>(&b1);
                 packed[c].z = *reinterpret_cast<unsigned*>(&b2); packed[c].w = *reinterpret_cast<unsigned*>(&b3);
             }
-            // O is stable and P's buffer free once the previous tile's second MMA is done
+            const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
             if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j + 3);
-            if (j > 0 && !at_wait(&sh->pv_done, (j - 1) & 1)) { if (lane == 0) atomicExch(p.error_word, 22); ok = false; break; }
-            if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j + 4);
-            at_fence_after();
             if (__any_sync(0xffffffffu, factor != 1.0f)) {
+                // O may be touched once the previous tile's second MMA is done.  (P needs no such wait: it goes
+                // over this tile's own scores.  The barrier is at most one phase ahead of the awaited one, as
+                // the next second MMA cannot be issued before this warp has published P.)
+                if (!at_wait(&sh->pv_done, (j - 1) & 1)) { if (lane == 0) atomicExch(p.error_word, 22); ok = false; break; }
+                at_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < AT_D / 32; ++c) {
                     unsigned r[32];
@@ -430,13 +445,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     words[4 * c + 2] = packed[c].z; words[4 * c + 3] = packed[c].w;
                 }
                 static_assert(AT_N == 64, "one 32-column store per row");
-                at_tmem_st32(tmem_s[buf] + lane_base, words);
+                at_tmem_st32(tmem_s(buf) + lane_base, words);
                 at_wait_st();
             }
             if (j == n_tiles - 1) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the zeroed value rows
             at_fence_before();
             __syncwarp();
-            if (lane == 0) at_arrive(&sh->p_full);
+            if (lane == 0) at_arrive(&sh->p_full[j & 1]);
             if (warp == 2 && lane == 0) AT_STAMP(2, 6 * j + 5);
         }
         if (ok) {
@@ -542,6 +557,6 @@ extern "C" int qil_attn_tc_prefill(const void* q, const void* kv, void* out, con
         if (e != cudaSuccess) QIL_REFUSE("attn_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    attn_tc_kernel<<<dim3(n_q_heads, n_tiles), 192, smem, stream>>>(map_q, map_kv, p, (const int4*)tile_info);
+    attn_tc_kernel<<<dim3(n_q_heads, n_tiles), AT_THREADS, smem, stream>>>(map_q, map_kv, p, (const int4*)tile_info);
     QIL_CHECK_LAUNCH();
 }
