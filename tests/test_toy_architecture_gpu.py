@@ -3,7 +3,8 @@ to the framework's files.  It is a toy, not anyone's model.  Its layers differ i
 
   0  a mixer with a state of its own (a decaying running sum kept in a per-request slot)
   1  full attention with q/k norms and full rotation
-  2  attention with a window of 20 positions and rotation of half of each head only; its feed-forward is
+  2  attention with a window of 20 positions and a position encoding of the test's own: half of each head is
+     rotated, by angles of positions squeezed by a factor plus a phase per frequency; its feed-forward is
      routed: a float32 router picks two of three small experts per token
   3  attention without k/v projections that reads the pages layer 1 wrote
 
@@ -32,6 +33,7 @@ class ToyConfig:
     head_dim: int = 16
     window: int = 20
     partial_rotary: int = 8
+    squeeze: float = 2.5
     theta: float = 10000.0
     eps: float = 1e-5
     inner: int = 72
@@ -51,8 +53,25 @@ class ToyConfig:
         return asdict(self) | {"architectures": [self.architecture], "model_type": self.model_type}
 
 
+def squeezed_angles(positions, rotary_dim, theta, squeeze):
+    """angle[p, j] = p / squeeze / theta^(2j / rotary_dim) + 0.1 j: the toy's own position encoding."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
+    return positions.float()[:, None] / squeeze * inv_freq[None, :] + 0.1 * torch.arange(rotary_dim // 2).float()
+
+
 def make_parts():
-    from qwen_inference_lab_b200.parts import FeedForward, Mixer, Param, StateSpec
+    from qwen_inference_lab_b200.parts import FeedForward, Mixer, Param, PositionEncoding, StateSpec
+
+    class SqueezedRotation(PositionEncoding):
+        """Another position encoding is another table of cosines and sines."""
+        graph_safe = True
+
+        def __init__(self, rotary_dim, theta, squeeze, max_positions):
+            self.rotary_dim, self.theta, self.squeeze, self.max_positions = rotary_dim, theta, squeeze, max_positions
+
+        def finalize(self, device, dtype):
+            angles = squeezed_angles(torch.arange(self.max_positions), self.rotary_dim, self.theta, self.squeeze)
+            self.table = torch.cat((angles.cos(), angles.sin()), dim=-1).to(dtype).float().contiguous().to(device)
 
     class RoutedFeedForward(FeedForward):
         """Router logits in float32, softmax over the chosen experts, tokens gathered per expert and
@@ -112,13 +131,13 @@ def make_parts():
             y = (h_all @ self.w_out.data.float().t()).to(x.dtype)
             return y if residual is None else (residual.float() + y.float()).to(x.dtype)
 
-    return RunningStateMixer, RoutedFeedForward
+    return RunningStateMixer, RoutedFeedForward, SqueezedRotation
 
 
 def build_toy(config):
     from qwen_inference_lab_b200.parts import (DecoderModel, GatedMLP, GroupedQueryAttention, LayerCall, Linear,
                                                PreNormBlock, RMSNorm, RotaryEmbedding, TokenEmbedding)
-    RunningStateMixer, RoutedFeedForward = make_parts()
+    RunningStateMixer, RoutedFeedForward, SqueezedRotation = make_parts()
     w, d = config.width, config.head_dim
     def block(i, mixer, routed=False):
         feed_forward = RoutedFeedForward(w, config.expert_inner, config.experts, config.experts_per_token,
@@ -133,7 +152,8 @@ def build_toy(config):
         block(0, RunningStateMixer(w, config.state_width, config.decay, name="blocks.0.state")),
         block(1, attention(1, qk_norm_eps=config.eps, position=RotaryEmbedding(d, config.theta, config.max_positions))),
         block(2, attention(2, qk_norm_eps=config.eps, window=config.window, bias=True,
-                           position=RotaryEmbedding(config.partial_rotary, config.theta, config.max_positions)),
+                           position=SqueezedRotation(config.partial_rotary, config.theta, config.squeeze,
+                                                     config.max_positions)),
               routed=True),
         block(3, attention(3, reads_shared_cache=True, position=RotaryEmbedding(d, config.theta, config.max_positions))),
     ]
@@ -182,7 +202,8 @@ def toy_plain_logits(tokens, w, c: ToyConfig):
         return ff(0, x + torch.stack(rows) @ w["blocks.0.state.w_out"].t())
 
     def rotate_part(v, rotary_dim):
-        angles = plain.rotary_angles(positions, rotary_dim, c.theta)
+        angles = plain.rotary_angles(positions, rotary_dim, c.theta) if rotary_dim == c.head_dim else \
+            squeezed_angles(positions, rotary_dim, c.theta, c.squeeze)
         return torch.cat((plain.rotate(v[..., :rotary_dim], angles), v[..., rotary_dim:]), dim=-1)
 
     def attention_layer(i, x, norms, rotary_dim, window=0, shared=False, bias=False):
