@@ -119,19 +119,19 @@ __device__ __forceinline__ unsigned gsm_mul2(unsigned a, unsigned b) {
     return *reinterpret_cast<const unsigned*>(&r);
 }
 
-// NT: token tiles of 8.  NORM = 1: fused RMSNorm (see the top of the file).  XS = 1: activations travel through the ring with the weights.  (XS = 0 reads
-// them from global memory in the threads that need them; measured slower at every token count, because
-// those reads miss the small L1 left beside the ring and stall the warp.  Kept for comparison.)
-template <int NT, int XS, int NORM>
+// NT: token tiles of 8.  NORM = 1: fused RMSNorm (see the top of the file).  The activations travel through the
+// ring with the weights: reading them from global memory in the threads that need them was slower at every
+// token count, because those reads miss the small L1 left beside the ring and stall the warp.
+template <int NT, int NORM>
 __global__ void __launch_bounds__(GSM_WARPS * 32)
 gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const bf16* __restrict__ bias,
                     const bf16* residual, void* out, const bf16* __restrict__ norm_w, float norm_eps,
                     int M, int N, int K, int out_f32, int silu_pairs) {
     extern __shared__ __align__(128) unsigned char ring[];          // [STAGES][STAGE_BYTES]
-    constexpr int XROWS = XS ? 8 * NT : 0;
+    constexpr int XROWS = 8 * NT;
     constexpr int NORM_ROW = GSM_ROWS + XROWS;                      // the stage row of the norm weight
     constexpr int STAGE_BYTES = (GSM_ROWS + XROWS + NORM) * GSM_ROW_BYTES;
-    constexpr int STAGES = (XS && NT == 2) ? 3 : GSM_STAGES;
+    constexpr int STAGES = NT == 2 ? 3 : GSM_STAGES;
     __shared__ float red[GSM_WARPS][GSM_ROWS][8 * NT + 1];
     __shared__ float squares[GSM_WARPS][8 * NT];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -163,19 +163,11 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
     qil_release_consumer();
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (XS && s < stages_total)
+        if (s < stages_total)
             gsm_issue_rows<GSM_ROWS, GSM_ROWS + XROWS>(copy, s * STAGE_BYTES, s * GSM_STAGE_K);
         asm volatile("cp.async.commit_group;\n" ::);
     }
 
-    const bf16* xp[NT];
-    bool ok_x[NT];
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        const int token = 8 * j + g;
-        ok_x[j] = token < M;
-        xp[j] = x + (size_t)(ok_x[j] ? token : 0) * K + 8 * t;
-    }
     float acc[NT][4];
     // With the norm: X X^T of the token tile on the tensor cores, of which the diagonal is each token's
     // sum of squares (products of bfloat16 values are exact in float32, the sums are float32).
@@ -206,16 +198,10 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
         uint4 vx[GSM_RUNS][NT];
 #pragma unroll
         for (int r = 0; r < GSM_RUNS; ++r) {
-            const int k = s * GSM_STAGE_K + kw + r * 32;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                if (XS) {
-                    vx[r][j] = *reinterpret_cast<const uint4*>(stage + (GSM_ROWS + 8 * j + g) * GSM_ROW_BYTES
-                                                               + (kw + r * 32 + 8 * t) * 2);
-                } else {
-                    vx[r][j] = make_uint4(0u, 0u, 0u, 0u);
-                    if (ok_x[j] && k + 8 * t < K) vx[r][j] = *reinterpret_cast<const uint4*>(xp[j] + k);
-                }
+                vx[r][j] = *reinterpret_cast<const uint4*>(stage + (GSM_ROWS + 8 * j + g) * GSM_ROW_BYTES
+                                                           + (kw + r * 32 + 8 * t) * 2);
             }
             if (NORM) {
                 const uint4 vn = *reinterpret_cast<const uint4*>(stage + NORM_ROW * GSM_ROW_BYTES + (kw + r * 32 + 8 * t) * 2);
@@ -313,16 +299,16 @@ extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, 
     static bool configured = false;
     if (!configured) {
         cudaError_t e[4] = {
-            cudaFuncSetAttribute(gemm_small_m_kernel<1, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1),
-            cudaFuncSetAttribute(gemm_small_m_kernel<2, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2),
-            cudaFuncSetAttribute(gemm_small_m_kernel<1, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1n),
-            cudaFuncSetAttribute(gemm_small_m_kernel<2, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2n)};
+            cudaFuncSetAttribute(gemm_small_m_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1),
+            cudaFuncSetAttribute(gemm_small_m_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2),
+            cudaFuncSetAttribute(gemm_small_m_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1n),
+            cudaFuncSetAttribute(gemm_small_m_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2n)};
         for (int i = 0; i < 4; ++i)
             if (e[i] != cudaSuccess) QIL_REFUSE("gemm_small_m: cannot reserve %d bytes of shared memory", smem1n);
         configured = true;
     }
 #define GSM_LAUNCH(NT, NORM, SMEM)                                                                                  \
-    qil_launch_chained(gemm_small_m_kernel<NT, 1, NORM>, dim3(blocks), dim3(GSM_WARPS * 32), SMEM, stream,           \
+    qil_launch_chained(gemm_small_m_kernel<NT, NORM>, dim3(blocks), dim3(GSM_WARPS * 32), SMEM, stream,           \
                        (const bf16*)x, (const bf16*)W, (const bf16*)bias, (const bf16*)residual, out,                \
                        (const bf16*)norm_w, norm_eps, M, N, K, out_f32, silu_pairs)
     if (norm_w == nullptr) {
