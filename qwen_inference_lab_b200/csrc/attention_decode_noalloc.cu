@@ -51,6 +51,7 @@ extern "C" int qil_attn_decode_noalloc(const void* q, const void* kv, void* out,
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
     if (check_decode_span(span_len, n_spans)) return -1;
+    if (span_len <= 0) QIL_REFUSE("attention (no allocation): the span length must be positive (a multiple of %d)", KV_TILE);
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention (no allocation): decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
     const long long slots = (long long)n_decode * n_q_heads * n_spans;

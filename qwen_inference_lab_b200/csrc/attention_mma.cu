@@ -34,7 +34,7 @@ QIL_ERROR_STORAGE
 
 #define KV_TILE 64          // key positions per shared-memory tile
 #define Q_TILE 64           // query tokens per block (prompt portions)
-#define MAX_DECODE_SPAN 2048 // most key positions per block (single tokens)
+#define MAX_DECODE_SPAN 8192 // most key positions per block (single tokens)
 
 constexpr int D = QIL_HEAD_DIM;
 constexpr int LDS = D + 8;           // shared-memory row stride in elements: rows start 16 bytes apart mod 128
@@ -85,8 +85,6 @@ struct AttnParams {
     int table_stride;
     int n_q_heads, n_kv_heads, page_size, num_pages, window;
     float scale_log2;         // head_dim^-1/2 * log2(e)
-    int slots;                // single tokens: blocks of the span kernel that the GPU runs at a time
-    int blocks_per_span;      // single tokens: blocks that share a span index (tokens x kv heads x head chunks)
 };
 
 // Where the key row of position ``pos`` of one kv head starts, in units of 16 bytes from the layer's
@@ -292,44 +290,16 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
 }
 
 // ------------------------------------------------------------------ single tokens: how long a span
-// When the caller leaves the span length to the kernels (span_len 0), both kernels of the pair derive it
-// from the step's longest context (the fourth int of every decode_info entry) with a small cost model:
-// blocks run in waves of `slots`; a wave takes about (tiles per span + 2) tile times, the 2 standing for a
-// block's start-up; every further span costs a little in the merge.  The grid's span count is the cap.
-// A recorded graph can so be replayed while contexts grow, with the span that suits each step.
-// Every warp evaluates the candidates itself, one per lane (2048 / 64 = 32 candidates), and takes the
-// cheapest, the shortest among equals: a few dozen instructions, no shared memory, no barrier.
-//
-// The spans of a context are equal but for the last, which takes what is left and is shorter.  Blocks
-// are numbered span by span (the span index is the grid's slowest dimension), so the short last spans
-// start last: a few blocks more than the GPU runs at a time cost nothing if they are short spans that
-// find a slot as soon as the first short spans are done (`2 * (last + start-up)` below).
-static_assert(MAX_DECODE_SPAN / KV_TILE == 32, "one candidate span length per lane");
-#ifndef SPAN_STARTUP20
-#define SPAN_STARTUP20 40     // a block's start-up in 1/20 tile times
-#endif
-#ifndef SPAN_MERGE20
-#define SPAN_MERGE20 3        // what one more span costs the merge, in 1/20 tile times
-#endif
-__device__ __forceinline__ int pick_span_len(int max_context, int n_spans_cap, int blocks_per_span, int slots) {
-    const int tiles = max(1, (max_context + KV_TILE - 1) / KV_TILE);
-    const int span_tiles = (threadIdx.x & 31) + 1;
-    const int n_spans = (tiles + span_tiles - 1) / span_tiles;
-    const int last_tiles = tiles - (n_spans - 1) * span_tiles;
-    const long long whole = (long long)blocks_per_span * (n_spans - 1), all = whole + blocks_per_span;
-    const long long one = 20ll * span_tiles + SPAN_STARTUP20;
-    long long time;
-    if (all <= slots) time = one;
-    else if (blocks_per_span + 2 * whole <= 2ll * slots) time = max(one, 2 * (20ll * last_tiles + SPAN_STARTUP20));
-    else time = (all + slots - 1) / slots * one;
-    // in units of 1/20 tile time, as integers: comparisons are exact and the same in both kernels
-    const long long cost = time + (long long)SPAN_MERGE20 * n_spans;
-    const int key = (n_spans <= n_spans_cap && cost < (1 << 24)) ? (int)cost * 64 + span_tiles : 0x7fffffff;
-    // cost first, then the shorter span
-    int best = key;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
-    return (best == 0x7fffffff ? MAX_DECODE_SPAN / KV_TILE : (best & 63)) * KV_TILE;
+// With a negative span length the caller fixes the number of spans (the grid's) and leaves their length to
+// the kernels: both kernels of the pair cut the step's longest context (the fourth int of every decode_info
+// entry) into n_spans equal runs of whole tiles.  A recorded graph can so be replayed while contexts grow:
+// every block of the grid keeps a share of the work, whatever the context (a span that nobody needs would
+// still take a slot away from the others when it starts).  Blocks are numbered span by span (the span index
+// is the grid's slowest dimension), so the short last spans start last.
+__device__ __forceinline__ int span_len_of(int longest_context, int n_spans, int at_most) {
+    const int tiles = max(1, (longest_context + KV_TILE - 1) / KV_TILE);
+    const int span_len = (tiles + n_spans - 1) / n_spans * KV_TILE;
+    return min(span_len, at_most);        // the caller sized shared memory for `at_most`
 }
 
 // ------------------------------------------------------------------ single tokens: the projection's tail
@@ -443,12 +413,12 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     const int chunks = (group + 15) / 16;
     const int kv_head = blockIdx.x / chunks, g0 = (blockIdx.x % chunks) * 16;
     const int gcount = min(16, group - g0);
-    const int span = blockIdx.z, d_idx = blockIdx.y;     // the span index varies slowest: see pick_span_len
+    const int span = blockIdx.z, d_idx = blockIdx.y;     // the span index varies slowest: see span_len_of
     const int4 info = decode_info[d_idx];
     const int n = info.x, pos = info.y;
     const int hi = pos;
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    const int span_len = span_len_arg > 0 ? span_len_arg : pick_span_len(info.w, n_spans, p.blocks_per_span, p.slots);
+    const int span_len = span_len_arg > 0 ? span_len_arg : span_len_of(info.w, n_spans, -span_len_arg);
     const int k_begin = span * span_len;
     if (k_begin > hi || k_begin + span_len <= lo) return;    // the merge skips the same spans
     const int* table = p.block_table + (size_t)info.z * p.table_stride;
@@ -579,7 +549,7 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
         __syncwarp();                // every lane has read the keys: their rows take tile t + 2
         if (tile + 2 <= last_tile) issue_rows(off2, my_k + buf * BUFFER, 0);
         cp_async_commit();
-        float tmax = -INFINITY;     // every row is the same position: one mask for all
+        // every row is the same position: one mask for all
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
@@ -591,7 +561,6 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
         }
         float tmax_a = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
         float tmax_b = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-        (void)tmax;
         tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 1));
         tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 2));
         tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 1));
@@ -675,7 +644,7 @@ attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, con
     const int4 info = decode_info[d_idx];
     const int n = info.x, pos = info.y;
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    const int span_len = span_len_arg > 0 ? span_len_arg : pick_span_len(info.w, n_spans, p.blocks_per_span, p.slots);
+    const int span_len = span_len_arg > 0 ? span_len_arg : span_len_of(info.w, n_spans, -span_len_arg);
     const int s_lo = lo / span_len;
     int s_hi = pos / span_len;
     if (s_hi >= n_spans) s_hi = n_spans - 1;   // cannot happen when the host sized n_spans for the batch
@@ -723,8 +692,6 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.slots = 1;
-    p.blocks_per_span = 1;
     return 0;
 }
 
@@ -736,7 +703,8 @@ static int decode_smem_bytes(int span_len, int page_size) {
 }
 
 static int check_decode_span(int span_len, int n_spans) {
-    if (span_len != 0 && (span_len < KV_TILE || span_len > MAX_DECODE_SPAN || span_len % KV_TILE))
+    const int length = span_len < 0 ? -span_len : span_len;      // negative: the longest the kernels may choose
+    if (length < KV_TILE || length > MAX_DECODE_SPAN || length % KV_TILE)
         QIL_REFUSE("attention: a span of %d positions; spans are multiples of %d up to %d", span_len, KV_TILE, MAX_DECODE_SPAN);
     if (n_spans <= 0) QIL_REFUSE("attention: n_spans %d", n_spans);
     return 0;
@@ -768,9 +736,10 @@ extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const 
 
 // decode_info: int32 [n_decode, 4] = (token, its absolute position, block-table row, 0).
 // Scratch: part_o needs n_decode * Hq * n_spans * D floats, part_ml n_decode * Hq * n_spans * 2 floats.
-// n_spans * span_len must cover the longest context of the batch (max position + 1).  span_len 0 leaves the
-// span length to the kernels: the fourth int of every decode_info entry must then hold the step's longest
-// context, and n_spans * 2048 must cover it; n_spans caps the number of spans used.
+// n_spans * span_len must cover the longest context of the batch (max position + 1).
+// A negative span_len leaves the length to the kernels (see span_len_of): the fourth int of every decode_info
+// entry must then hold the step's longest context, and -span_len is the longest span that may come of it
+// (n_spans * -span_len covers the longest context the launch, or a graph recorded from it, will ever see).
 static int launch_decode(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
                          float* part_o, float* part_ml, int n_spans, int span_len,
                          const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
@@ -785,26 +754,13 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention: decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
     if (n_decode > 65535 || n_spans > 65535) QIL_REFUSE("attention: grid too large");
-    const int smem = decode_smem_bytes(span_len > 0 ? span_len : MAX_DECODE_SPAN, page_size);
+    const int smem = decode_smem_bytes(span_len > 0 ? span_len : -span_len, page_size);
     static int configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_span_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = smem;
     }
-    static int sm_count = 0, per_sm = 0;
-    if (sm_count == 0) {
-        int device = 0;
-        if (cudaGetDevice(&device) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
-            sm_count = 148;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_span_kernel, 128, smem) != cudaSuccess || per_sm <= 0) {
-            (void)cudaGetLastError();
-            per_sm = 1;
-        }
-    }
-    p.slots = sm_count * per_sm;
-    p.blocks_per_span = n_decode * n_kv_heads * chunks;
     qil_launch_chained(attn_decode_span_kernel, dim3(n_kv_heads * chunks, n_decode, n_spans), dim3(128), smem, stream,
                        p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len, tail);
     {

@@ -187,7 +187,7 @@ class StepRunner:
         host = dict(seg_row=rows, seg_start=seg_start, seg_len=lens, seg_pos0=starts)
         return packed, offsets, host, n, s, int((starts + lens).max())
 
-    def _context(self, offsets, host, n, s, max_context):
+    def _context(self, offsets, host, n, s, max_context, min_context=0):
         def section(name):
             begin, count = offsets[name]
             return self._meta_dev[begin:begin + count]
@@ -199,7 +199,7 @@ class StepRunner:
             n_decode=offsets["decode_info"][1] // 4, decode_info=section("decode_info"),
             n_big_tiles=offsets["big_tile_info"][1] // 4, big_tile_info=section("big_tile_info"),
             n_rest_tiles=offsets["rest_tile_info"][1] // 4, rest_tile_info=section("rest_tile_info"),
-            max_context=max_context, h_seg_row=host["seg_row"], h_seg_start=host["seg_start"],
+            max_context=max_context, min_context=min_context, h_seg_row=host["seg_row"], h_seg_start=host["seg_start"],
             h_seg_len=host["seg_len"], h_seg_pos0=host["seg_pos0"], extras=self._extras)
 
     def _upload(self, packed):
@@ -265,7 +265,7 @@ class StepRunner:
         key = (n, bucket)
         record = self._graphs.get(key)
         if record is None:
-            ctx = self._context(offsets, host, n, s, bucket)
+            ctx = self._context(offsets, host, n, s, bucket, min_context=bucket // 2 + 1 if bucket > 512 else 1)
             begin, count = offsets["logit_rows"]
             logit_rows = self._meta_dev[begin:begin + count]
             # one eager run first: libraries set up their workspaces outside the recording

@@ -16,7 +16,7 @@ from .ops import KernelError, _check, _p, _stream
 
 _libs: dict = {}
 KV_TILE = 64
-MAX_DECODE_SPAN = 2048
+MAX_DECODE_SPAN = 8192
 
 
 def supports(head_dim, n_q_heads, n_kv_heads) -> bool:
@@ -48,39 +48,48 @@ def _slots(head_dim) -> int:
     return _sm_count * max(1, min(3, (227 * 1024) // block_smem))
 
 
-def choose_span(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> int:
-    """Positions per block of the single-token kernel, from a small cost model.
+# The span model, in "tile times" (what a block takes to stream a 64-key tile).  Blocks run in waves of
+# (SMs x blocks per SM); a wave takes the tiles of a span plus SPAN_STARTUP for a block's start-up (its
+# description, page ids and first tile arrive one after the other); every span costs the merge SPAN_MERGE.
+# So the context is cut into as many spans as fill the GPU once, fewer when the requests are few.
+# Measured inside the recorded decode step (Qwen3-8B heads, context 8192, B200): batch 8 takes 4.84 ms with
+# 5 or 6 spans (320 or 384 of 444 slots), 4.97 with 4, 5.1 with 7 to 9 (a few blocks spill into a second
+# wave), 4.92 with 11 to 13; batch 1 is flat from 16 to 43 spans, batch 4 best at 11, batch 16 at 3 or 6.
+# Timed alone, without the projection before it and the chained launches around it, the same pair of
+# kernels prefers fewer, longer spans (256 blocks: two per SM); that did not carry over to the step.
+SPAN_STARTUP, SPAN_MERGE = 2.0, 0.15
 
-    Blocks run in waves of (SMs x blocks per SM); a wave takes about (tiles per span + 2) tile
-    times, the 2 standing for a block's start-up (its metadata, page ids and first tile arrive one
-    after the other); every further span also costs a little in the merge.  The span with the
-    lowest cost wins; measured on B200 at context 8192 this picks 1408 for batch 8 (384 blocks, one
-    wave: 54 us against 58-66 us for spans of 384 to 1024) and 1664 for batch 64.  The kernels hold the
-    same model (``pick_span_len``) and use it when they are given a span length of 0, with the step's
-    own longest context; this function serves callers that fix the span themselves.
-    """
+
+def _span_cost(tiles, n_spans, blocks_per_span, slots) -> float:
+    """Tile times of the kernel pair for a longest context of ``tiles`` tiles cut into ``n_spans`` spans."""
+    per_span = -(-tiles // n_spans)
+    n_spans = -(-tiles // per_span)                     # spans that hold anything
+    waves = -(-blocks_per_span * n_spans // slots)
+    return waves * (per_span + SPAN_STARTUP) + SPAN_MERGE * n_spans
+
+
+def plan_spans(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128, min_context=None):
+    """(n_spans, longest span) for steps whose longest context lies in [min_context, max_context]: the kernels
+    cut each step's own longest context into ``n_spans`` equal spans (a recorded graph is replayed while
+    contexts grow), so the count is chosen for both ends of the range; the longest span sizes shared memory."""
     blocks_per_span = n_decode * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16)
     slots = _slots(head_dim)
-    tiles = max(1, (max_context + KV_TILE - 1) // KV_TILE)
-    best, best_cost = 1, None
-    for span_tiles in range(1, MAX_DECODE_SPAN // KV_TILE + 1):
-        n_spans = (tiles + span_tiles - 1) // span_tiles
-        waves = (blocks_per_span * n_spans + slots - 1) // slots
-        cost = waves * (span_tiles + 2) + 0.15 * n_spans
+    hi = max(1, (max_context + KV_TILE - 1) // KV_TILE)
+    lo = max(1, min(hi, ((min_context or max_context) + KV_TILE - 1) // KV_TILE))
+    least = -(-hi // (MAX_DECODE_SPAN // KV_TILE))      # the longest span is a limit of the kernels
+    best, best_cost = None, None
+    for n_spans in range(least, max(least, min(hi, 256)) + 1):
+        cost = _span_cost(hi, n_spans, blocks_per_span, slots) / hi
+        if lo != hi:
+            cost += _span_cost(lo, min(n_spans, lo), blocks_per_span, slots) / lo
         if best_cost is None or cost < best_cost - 1e-9:
-            best, best_cost = span_tiles, cost
-    return best * KV_TILE
+            best, best_cost = n_spans, cost
+    return best, -(-hi // best) * KV_TILE
 
 
-def span_cap(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> int:
-    """The most spans the kernels may use for any context up to ``max_context`` when they choose the
-    span length themselves (the grid's first dimension, and what the scratch is sized for).  The cost
-    model never prefers a second wave of shorter spans to one wave, so one wave's worth of spans is
-    enough unless the longest span (2048 positions) forces more."""
-    slots, blocks_per_span = _slots(head_dim), n_decode * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16)
-    tiles = max(1, (max_context + KV_TILE - 1) // KV_TILE)
-    longest = MAX_DECODE_SPAN // KV_TILE
-    return min(tiles, max(-(-slots // blocks_per_span), -(-tiles // longest)) + 1)
+def choose_span(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> int:
+    """Positions per block of the single-token kernel for a step whose longest context is ``max_context``."""
+    return plan_spans(n_decode, n_q_heads, n_kv_heads, max_context, head_dim)[1]
 
 
 def decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim):
@@ -113,7 +122,9 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
 
 def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
            n_q_heads, n_kv_heads, head_dim, page_size, window, scale):
-    """decode_info int32 [n_decode * 4]: (token, its position, block-table row, 0) per single token."""
+    """decode_info int32 [n_decode * 4]: (token, its position, block-table row, the step's longest context)
+    per single token.  A negative ``span_len``: the kernels cut the step's longest context into ``n_spans``
+    equal spans of at most ``-span_len`` positions (see ``plan_spans``)."""
     lib = library(head_dim)
     _check(lib, lib.qil_attn_decode(
         _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), c_int(n_spans),
@@ -145,14 +156,15 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
     if rope_table is not None and (rope_table.dtype != torch.float32 or rope_table.shape[1] != rotary_dim
                                    or not rope_table.is_contiguous()):
         raise KernelError("attention: the rotary table must be float32 [positions, rotary_dim]")
-    # the kernels pick the span from the step's own longest context (decode_info carries it); ctx.max_context
-    # may be a recorded graph's upper bound and only caps the number of spans
-    span_len, n_spans = 0, span_cap(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim)
+    # the kernels cut the step's own longest context (decode_info carries it) into n_spans spans; ctx.max_context
+    # may be a recorded graph's upper bound, ctx.min_context its lower one
+    n_spans, longest_span = plan_spans(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
+                                       getattr(ctx, "min_context", 0) or None)
     part_o, part_ml = decode_scratch(ctx, ctx.n_decode, n_q_heads, n_spans, head_dim)
     lib = library(head_dim)
     _check(lib, lib.qil_attn_decode_qkv(
         _p(qkv), _p(cache.pages), _p(out), _p(ctx.decode_info), c_int(ctx.n_decode), _p(part_o), _p(part_ml),
-        c_int(n_spans), c_int(span_len), _p(cache.block_table), c_int(cache.block_table.shape[1]),
+        c_int(n_spans), c_int(-longest_span), _p(cache.block_table), c_int(cache.block_table.shape[1]),
         c_int(n_q_heads), c_int(n_kv_heads), c_int(own_kv_heads), c_int(cache.page_size),
         c_int(cache.pages.shape[0]), c_int(window), c_float(scale), _p(q_norm), _p(k_norm), c_float(float(eps)),
         _p(rope_table), c_int(rotary_dim if rope_table is not None else 0),
@@ -177,7 +189,8 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
         prefill(q, cache.pages, out, ctx.tile_info, ctx.n_tiles, cache.block_table, n_q_heads, n_kv_heads,
                 head_dim, cache.page_size, window, scale)
     if ctx.n_decode:
-        span_len, n_spans = 0, span_cap(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim)
+        n_spans, longest_span = plan_spans(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
+                                           getattr(ctx, "min_context", 0) or None)
         part_o, part_ml = decode_scratch(ctx, ctx.n_decode, n_q_heads, n_spans, head_dim)
-        decode(q, cache.pages, out, ctx.decode_info, ctx.n_decode, part_o, part_ml, n_spans, span_len,
+        decode(q, cache.pages, out, ctx.decode_info, ctx.n_decode, part_o, part_ml, n_spans, -longest_span,
                cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale)

@@ -157,6 +157,9 @@ class StepContext:
     n_decode: int
     decode_info: torch.Tensor        # [n_decode * 4]
     max_context: int                 # largest start+len over the batch's segments (host upper bound)
+    # a recorded graph is replayed with other contexts than the step it was recorded from: max_context is then
+    # the largest longest-context of those steps and min_context the smallest (0: this step only)
+    min_context: int = 0
     # the multi-token segments cut a second way: whole tiles of 128 tokens, and 64-token tiles for the rest
     n_big_tiles: int = 0
     big_tile_info: torch.Tensor = None    # [n_big_tiles * 4], same four ints as tile_info

@@ -227,9 +227,10 @@ def run_mma(q, pool, table, meta, n_q, n_kv, d, page, window, span_len=256):
     if decode_info:
         n_decode = len(decode_info) // 4
         longest = max(p0 + n for p0, n in zip(meta["seg_pos0"], meta["seg_len"]))
-        if span_len == 0:       # the kernels choose: every entry carries the longest context, the grid caps the spans
+        if span_len == 0:       # the kernels cut the longest context, which every entry carries, into the grid's spans
             decode_info[3::4] = [longest] * n_decode
-            n_spans = attention_mma.span_cap(n_decode, n_q, n_kv, longest + 300, d)   # as under a recorded graph's bound
+            n_spans, span_len = attention_mma.plan_spans(n_decode, n_q, n_kv, longest + 300, d, longest // 2)   # as under a recorded graph's bounds
+            span_len = -span_len
         else:
             n_spans = (longest + span_len - 1) // span_len + 1   # one spare span
         part_o = torch.full((n_decode * n_q * n_spans * d,), float("nan"), dtype=torch.float32).cuda()
@@ -263,14 +264,18 @@ def test_attention_tensor_core(case):
         close(out, last_expected, torch.bfloat16, scale=2)
 
 
-def test_span_choice_fills_the_gpu_and_stays_legal():
+def test_span_plan_stays_legal():
     from qwen_inference_lab_b200.kernels import attention_mma
-    for n_decode, ctx in ((1, 8192), (8, 8192), (64, 8192), (1, 100), (256, 40000), (3, 1)):
-        span = attention_mma.choose_span(n_decode, 32, 8, ctx)
-        assert span % 64 == 0 and 64 <= span <= attention_mma.MAX_DECODE_SPAN
-    assert attention_mma.choose_span(1, 32, 8, 8192) < attention_mma.choose_span(64, 32, 8, 8192)
-    # batch 8 at context 8192: whole waves of the 148 x 3 blocks a B200 holds (6 or 13 spans of 64 blocks)
-    assert attention_mma.choose_span(8, 32, 8, 8192) in (640, 1408)
+    for n_decode, lo, hi in ((1, 8192, 8192), (8, 8193, 16384), (64, 8192, 8192), (1, 1, 100), (256, 40000, 40000),
+                             (3, 1, 1), (2, 65537, 131072), (1, 1, 512)):
+        n_spans, longest = attention_mma.plan_spans(n_decode, 32, 8, hi, 128, lo)
+        assert n_spans >= 1 and longest % 64 == 0 and 64 <= longest <= attention_mma.MAX_DECODE_SPAN
+        assert n_spans * longest >= hi                          # the spans cover the longest context
+        assert (n_spans - 1) * longest < hi + 64 * n_spans      # and are not longer than that takes
+        assert attention_mma.choose_span(n_decode, 32, 8, hi) % 64 == 0
+    # few requests are cut into more spans than many; one request of a short context is not cut into hundreds
+    assert attention_mma.plan_spans(1, 32, 8, 8192)[0] > attention_mma.plan_spans(16, 32, 8, 8192)[0]
+    assert attention_mma.plan_spans(1, 32, 8, 1024)[0] <= 16
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,lengths,page,window,rotary,norms,own", [
@@ -299,7 +304,12 @@ def test_attention_single_tokens_from_the_projection(n_q, n_kv, d, lengths, page
     decode_info = as_int([v for i in range(n) for v in (i, lengths[i] - 1, meta["seg_row"][i], longest)])
     for span_len, bound in ((64, longest), (256, longest), (2048, longest), (0, longest), (0, 2 * longest + 100)):
         # span_len 0: the kernels choose the span; ``bound`` stands for a recorded graph's upper bound
-        n_spans = (longest + span_len - 1) // span_len if span_len else attention_mma.span_cap(n, n_q, n_kv, bound, d)
+        if span_len == 0:
+            n_spans, span_len = attention_mma.plan_spans(n, n_q, n_kv, bound, d, longest)
+            span_len = -span_len
+            planned = True
+        else:
+            n_spans, planned = (longest + span_len - 1) // span_len, False
         scratch = lambda: (torch.full((n * n_q * n_spans * d,), float("nan")).cuda(),
                            torch.full((n * n_q * n_spans * 2,), float("nan")).cuda())
         # the two kernels
@@ -314,7 +324,7 @@ def test_attention_single_tokens_from_the_projection(n_q, n_kv, d, lengths, page
         pages_b = pool.cuda().clone()
         out_b = torch.full((n, n_q * d), float("nan"), dtype=torch.bfloat16).cuda()
         part_o, part_ml = scratch()
-        ctx = SimpleNamespace(n_tokens=n, n_decode=n, n_tiles=0, max_context=bound, decode_info=decode_info,
+        ctx = SimpleNamespace(n_tokens=n, n_decode=n, n_tiles=0, max_context=bound, min_context=longest, decode_info=decode_info,
                               extras={"attn_decode_scratch": (part_o, part_ml)}, device=qkv.device)
         cache = SimpleNamespace(pages=pages_b, block_table=table.cuda(), page_size=page)
         assert attention_mma.projection_tail_usable(ctx, qkv, cache, n_q, n_kv, d, rotary, (q_norm, k_norm))
@@ -322,7 +332,7 @@ def test_attention_single_tokens_from_the_projection(n_q, n_kv, d, lengths, page
                                         k_norm, eps, rope, rotary)
         torch.cuda.synchronize()
         assert not torch.isnan(out_b).any()
-        if span_len == 0:
+        if planned:
             assert torch.equal(out_a, out_b)        # the same spans in both: the same bits
         else:
             close(out_b, out_a, torch.bfloat16, scale=2)
