@@ -7,6 +7,7 @@ shared by all layers.
 """
 from __future__ import annotations
 
+import functools
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -68,14 +69,9 @@ def _span_cost(tiles, n_spans, blocks_per_span, slots) -> float:
     return waves * (per_span + SPAN_STARTUP) + SPAN_MERGE * n_spans
 
 
-def plan_spans(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128, min_context=None):
-    """(n_spans, longest span) for steps whose longest context lies in [min_context, max_context]: the kernels
-    cut each step's own longest context into ``n_spans`` equal spans (a recorded graph is replayed while
-    contexts grow), so the count is chosen for both ends of the range; the longest span sizes shared memory."""
-    blocks_per_span = n_decode * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16)
-    slots = _slots(head_dim)
-    hi = max(1, (max_context + KV_TILE - 1) // KV_TILE)
-    lo = max(1, min(hi, ((min_context or max_context) + KV_TILE - 1) // KV_TILE))
+@functools.lru_cache(maxsize=4096)
+def _plan_tiles(blocks_per_span, slots, lo, hi) -> int:
+    """The number of spans with the lowest cost per tile at both ends of [lo, hi] tiles of longest context."""
     least = -(-hi // (MAX_DECODE_SPAN // KV_TILE))      # the longest span is a limit of the kernels
     best, best_cost = None, None
     for n_spans in range(least, max(least, min(hi, 256)) + 1):
@@ -84,7 +80,19 @@ def plan_spans(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128, min_c
             cost += _span_cost(lo, min(n_spans, lo), blocks_per_span, slots) / lo
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = n_spans, cost
-    return best, -(-hi // best) * KV_TILE
+    return best
+
+
+def plan_spans(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128, min_context=None):
+    """(n_spans, longest span) for steps whose longest context lies in [min_context, max_context]: the kernels
+    cut each step's own longest context into ``n_spans`` equal spans (a recorded graph is replayed while
+    contexts grow), so the count is chosen for both ends of the range; the longest span sizes shared memory.
+    Eager steps ask once per layer and step: the answer is remembered per (blocks, tiles)."""
+    blocks_per_span = n_decode * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16)
+    hi = max(1, (max_context + KV_TILE - 1) // KV_TILE)
+    lo = max(1, min(hi, ((min_context or max_context) + KV_TILE - 1) // KV_TILE))
+    n_spans = _plan_tiles(blocks_per_span, _slots(head_dim), lo, hi)
+    return n_spans, -(-hi // n_spans) * KV_TILE
 
 
 def choose_span(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> int:

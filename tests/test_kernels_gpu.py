@@ -264,20 +264,6 @@ def test_attention_tensor_core(case):
         close(out, last_expected, torch.bfloat16, scale=2)
 
 
-def test_span_plan_stays_legal():
-    from qwen_inference_lab_b200.kernels import attention_mma
-    for n_decode, lo, hi in ((1, 8192, 8192), (8, 8193, 16384), (64, 8192, 8192), (1, 1, 100), (256, 40000, 40000),
-                             (3, 1, 1), (2, 65537, 131072), (1, 1, 512)):
-        n_spans, longest = attention_mma.plan_spans(n_decode, 32, 8, hi, 128, lo)
-        assert n_spans >= 1 and longest % 64 == 0 and 64 <= longest <= attention_mma.MAX_DECODE_SPAN
-        assert n_spans * longest >= hi                          # the spans cover the longest context
-        assert (n_spans - 1) * longest < hi + 64 * n_spans      # and are not longer than that takes
-        assert attention_mma.choose_span(n_decode, 32, 8, hi) % 64 == 0
-    # few requests are cut into more spans than many; one request of a short context is not cut into hundreds
-    assert attention_mma.plan_spans(1, 32, 8, 8192)[0] > attention_mma.plan_spans(16, 32, 8, 8192)[0]
-    assert attention_mma.plan_spans(1, 32, 8, 1024)[0] <= 16
-
-
 @pytest.mark.parametrize("n_q,n_kv,d,lengths,page,window,rotary,norms,own", [
     (32, 8, 128, [2100, 64, 641], 16, 0, 128, True, True),
     (6, 3, 80, [520, 130, 1], 16, 64, 40, True, True),        # half of the head rotated, a window, a first token
