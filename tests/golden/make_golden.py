@@ -62,4 +62,6 @@ def main(reference_root):
 
 
 if __name__ == "__main__":
-    main(Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference"))
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/qwen-inference-lab")
+    main(Path(sys.argv[1]))
