@@ -651,23 +651,47 @@ attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, con
     const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
     qil_wait_for_producer();
     qil_release_consumer();
-    // every thread reads the few (max, sum) pairs itself: the loads are independent and overlap
-    float mx = -INFINITY;
-    for (int s = s_lo; s <= s_hi; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
-    const float ms = (mx == -INFINITY) ? 0.f : mx;
-    float sum = 0.f;
-    float acc[(D + 127) / 128];
+    // Spans are taken eight at a time: their (max, sum) pairs and this thread's columns of their partial
+    // outputs are all asked for before any is used, so a batch costs one trip to L2 instead of one for the
+    // maxima and another for the outputs; batches are folded into the running result as in the kernels above
+    // (rescale by exp2(old max - new max)).  The order of the sums is fixed by the span numbers.
+    constexpr int COLS = (D + 127) / 128, BATCH = 8;
+    float mx = -INFINITY, sum = 0.f;
+    float acc[COLS];
 #pragma unroll
-    for (int i = 0; i < (D + 127) / 128; ++i) acc[i] = 0.f;
-#pragma unroll 8
-    for (int s = s_lo; s <= s_hi; ++s) {
-        const float f = exp2f(part_ml[(base + s) * 2] - ms);
-        sum += f * part_ml[(base + s) * 2 + 1];
+    for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
+    for (int s0 = s_lo; s0 <= s_hi; s0 += BATCH) {
+        float m[BATCH], l[BATCH], o[BATCH][COLS];
 #pragma unroll
-        for (int i = 0; i < (D + 127) / 128; ++i) {
-            const int col = threadIdx.x + i * 128;
-            if (col < D) acc[i] += f * part_o[(base + s) * D + col];
+        for (int j = 0; j < BATCH; ++j) {
+            const bool live = s0 + j <= s_hi;
+            const size_t slot = base + (live ? s0 + j : s_lo);
+            const float2 ml = *reinterpret_cast<const float2*>(part_ml + slot * 2);
+            m[j] = live ? ml.x : -INFINITY;
+            l[j] = ml.y;
+#pragma unroll
+            for (int i = 0; i < COLS; ++i) {
+                const int col = threadIdx.x + i * 128;
+                o[j][i] = col < D ? part_o[slot * D + col] : 0.f;
+            }
         }
+        float batch_max = m[0];
+#pragma unroll
+        for (int j = 1; j < BATCH; ++j) batch_max = fmaxf(batch_max, m[j]);
+        const float new_max = fmaxf(mx, batch_max);
+        const float ms = (new_max == -INFINITY) ? 0.f : new_max;
+        const float keep = exp2f(mx - ms);               // 0 for the first batch (mx = -inf)
+        sum *= keep;
+#pragma unroll
+        for (int i = 0; i < COLS; ++i) acc[i] *= keep;
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+            const float f = exp2f(m[j] - ms);            // 0 for a slot past the last span
+            sum += f * l[j];
+#pragma unroll
+            for (int i = 0; i < COLS; ++i) acc[i] += f * o[j][i];
+        }
+        mx = new_max;
     }
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
 #pragma unroll
