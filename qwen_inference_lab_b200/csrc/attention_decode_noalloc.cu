@@ -17,8 +17,9 @@ static float* noalloc_scratch_address[QIL_NOALLOC_MAX_DEVICES];   // per device,
 
 extern "C" long long qil_attn_decode_noalloc_max_floats(void) { return QIL_NOALLOC_MAX_FLOATS; }
 
-// Once per device, with that device current: the array's address and the span kernel's
-// shared-memory limit.  Neither allocates.
+// Once per device, with that device current: the array's address.  The span kernel's shared-memory
+// limit is kept by ensure_decode_smem, which the regular entry points use too, so whichever of them
+// runs first or last the limit only grows.  Neither call allocates.
 static int noalloc_setup(int smem, float** scratch) {
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
@@ -31,13 +32,9 @@ static int noalloc_setup(int smem, float** scratch) {
             snprintf(qil_error_text, sizeof(qil_error_text), "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
             return e != cudaSuccess ? (int)e : -1;
         }
-        e = cudaFuncSetAttribute(attn_decode_span_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) {
-            snprintf(qil_error_text, sizeof(qil_error_text), "cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-            return (int)e;
-        }
         noalloc_scratch_address[device] = address;
     }
+    if (ensure_decode_smem(attn_decode_span_kernel, smem)) return -1;
     *scratch = noalloc_scratch_address[device];
     return 0;
 }

@@ -17,7 +17,8 @@
  * caller's; decode_info holds four ints per token (its row in q and out, its
  * absolute position, its row of the block table, 0); span_len is the number of
  * key positions one block covers (a multiple of 64) and n_spans * span_len must
- * reach the longest context.
+ * reach the longest context; a token whose position lies beyond n_spans * span_len
+ * gets a row of NaN, not a softmax over a shortened context.
  *
  * Limits and rules.
  *  - The scratch array holds qil_attn_decode_noalloc_max_floats() floats (16 MiB;
@@ -28,7 +29,12 @@
  *  - It calls no cudaMalloc, cudaFree or any routine that allocates.
  *  - The first call on each device looks up the array's device address and sets
  *    a kernel attribute; make that first call outside any stream capture, with
- *    the device it is meant for current.
+ *    the device it is meant for current.  That attribute (the kernel's shared-memory
+ *    limit) is shared with qil_attn_decode of the same library and only ever raised,
+ *    so the two may be called in any order.
+ *  - Host threads: the per-device set-up and the error text are plain statics.  Call
+ *    this function (and the other entry points of the library) from one host thread
+ *    at a time per device, or put your own lock around them.
  *  - All calls share the one array, and it keeps what the last call left in it.
  *    Nothing in it has to start at zero: every slot a call reads, that call wrote
  *    first.  Two calls whose kernels overlap on the GPU (different streams, no

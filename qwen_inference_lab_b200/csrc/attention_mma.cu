@@ -647,7 +647,10 @@ attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, con
     const int span_len = span_len_arg > 0 ? span_len_arg : span_len_of(info.w, n_spans, -span_len_arg);
     const int s_lo = lo / span_len;
     int s_hi = pos / span_len;
-    if (s_hi >= n_spans) s_hi = n_spans - 1;   // cannot happen when the host sized n_spans for the batch
+    // n_spans * span_len does not reach this token's position: the span kernel never saw its last keys, and a
+    // softmax over a shortened context would look like a result.  The row is filled with NaN instead.
+    const bool uncovered = s_hi >= n_spans;
+    if (uncovered) s_hi = n_spans - 1;
     const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
     qil_wait_for_producer();
     qil_release_consumer();
@@ -697,7 +700,9 @@ attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, con
 #pragma unroll
     for (int i = 0; i < (D + 127) / 128; ++i) {
         const int col = threadIdx.x + i * 128;
-        if (col < D) p.out[((size_t)n * p.n_q_heads + head) * D + col] = __float2bfloat16_rn(acc[i] * inv);
+        if (col < D)
+            p.out[((size_t)n * p.n_q_heads + head) * D + col] =
+                __float2bfloat16_rn(uncovered ? __int_as_float(0x7fc00000) : acc[i] * inv);
     }
 }
 
@@ -724,6 +729,25 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
 static int decode_smem_bytes(int span_len, int page_size) {
     const int tile_bytes = (16 + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
     return tile_bytes + (span_len / page_size + 3) * (int)sizeof(int);
+}
+
+// The span kernel's dynamic shared-memory limit is a setting of the function on a device: every entry point
+// that launches the kernel goes through here, so the limit is only ever raised.  One slot per device
+// ordinal; not safe for host threads that call these entry points at the same time.
+#define QIL_ATTN_MAX_DEVICES 64
+static int decode_smem_configured[QIL_ATTN_MAX_DEVICES];
+template <typename Kernel>
+static int ensure_decode_smem(Kernel kernel, int smem) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) QIL_REFUSE("attention: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (device < 0 || device >= QIL_ATTN_MAX_DEVICES) QIL_REFUSE("attention: device %d is out of range", device);
+    if (smem > decode_smem_configured[device]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        decode_smem_configured[device] = smem;
+    }
+    return 0;
 }
 
 static int check_decode_span(int span_len, int n_spans) {
@@ -779,12 +803,7 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
     if (n_decode > 65535 || n_spans > 65535) QIL_REFUSE("attention: grid too large");
     const int smem = decode_smem_bytes(span_len > 0 ? span_len : -span_len, page_size);
-    static int configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_span_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = smem;
-    }
+    if (ensure_decode_smem(attn_decode_span_kernel, smem)) return -1;
     qil_launch_chained(attn_decode_span_kernel, dim3(n_kv_heads * chunks, n_decode, n_spans), dim3(128), smem, stream,
                        p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len, tail);
     {

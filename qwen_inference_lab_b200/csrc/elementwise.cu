@@ -273,3 +273,40 @@ extern "C" int qil_cast(const void* src, int src_dtype, void* dst, int dst_dtype
         cast_kernel<T, W><<<blocks, 256, 0, stream>>>((const W*)src, (T*)dst, (size_t)total));
     QIL_CHECK_LAUNCH();
 }
+
+// ---------------------------------------------------------------- random weights
+// out[i] = mean + std * z(seed, i) with z close to N(0, 1): the sum of twelve 16-bit uniforms drawn from
+// three rounds of a 64-bit counter hash, centred and divided by 65536.  Integer arithmetic and three
+// correctly rounded float operations only, so the host twin (weights/random_init.py) gives the same bits.
+__device__ __forceinline__ unsigned long long fill_hash(unsigned long long seed, unsigned long long counter) {
+    unsigned long long z = seed + (counter + 1ull) * 0x9E3779B97F4A7C15ull;
+    z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull;
+    z ^= z >> 27; z *= 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return z;
+}
+
+template <typename T>
+__global__ void fill_normal_kernel(T* __restrict__ out, long long total, unsigned long long seed, float std,
+                                   float mean) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        int sum = 0;
+#pragma unroll
+        for (int round = 0; round < 3; ++round) {
+            const unsigned long long h = fill_hash(seed, 3ull * (unsigned long long)i + round);
+            sum += (int)(h & 0xFFFFull) + (int)((h >> 16) & 0xFFFFull) + (int)((h >> 32) & 0xFFFFull) + (int)(h >> 48);
+        }
+        const float z = __fmul_rn((float)(sum - 393210), 1.0f / 65536.0f);
+        out[i] = from_f32<T>(__fadd_rn(__fmul_rn(z, std), mean));
+    }
+}
+
+extern "C" int qil_fill_normal(void* out, int out_dtype, long long total, unsigned long long seed, float std,
+                               float mean, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const long long blocks = (total + 255) / 256;
+    const int grid = (int)(blocks < 148 * 16 ? blocks : 148 * 16);
+    QIL_DISPATCH_1(out_dtype, fill_normal_kernel<T><<<grid, 256, 0, stream>>>((T*)out, total, seed, std, mean));
+    QIL_CHECK_LAUNCH();
+}

@@ -22,7 +22,6 @@ from __future__ import annotations
 from time import perf_counter
 
 from ..cache import CacheManager
-from ..kernels import attention_tc, gemm_tc
 from ..sampling import Sampler
 from .scheduler import Request, Scheduler
 from .step import PENDING, StepEntry, StepRunner
@@ -141,9 +140,7 @@ class Engine:
         requests = self.scheduler.requests
         try:
             tokens = self.sampler.finish(queued["ticket"]) if queued["ticket"] is not None else []
-            if sum(len(work.tokens) for work in plan) >= gemm_tc.MIN_ROWS:
-                gemm_tc.check()      # the tensor-memory kernels' bounded waits report through error words
-                attention_tc.check()
+            self.runner.check(wait=not self.overlap)     # kernels with bounded waits report through error words
         except Exception as error:
             self._fail(plan, error)
             if quiet:

@@ -44,7 +44,6 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     import torch
 
     from ..cache import CacheManager
-    from ..kernels import attention_tc, gemm_tc
     from ..loading import load_model, resolve_dtype
     from .step import StepEntry, StepRunner
 
@@ -72,8 +71,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
             logits = runner.run(entries)
             if logits is not None:
                 data = logits.detach().to(torch.float32).cpu().contiguous().numpy()
-                gemm_tc.check()
-                attention_tc.check()
+                runner.check()
                 data.astype("<f4", copy=False).tofile(args.out / f"{step['step']}.f32")
         for request_id in step.get("end", []):
             if request_id in cache.rows:

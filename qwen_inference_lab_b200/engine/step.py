@@ -20,11 +20,8 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from ..parts.base import StepContext
+from ..parts.base import PlanView, Segments, StepContext
 from ..utils.staging import PinnedRing
-
-QUERY_TILE = 64          # tokens per query tile of the prompt-portion attention kernel
-BIG_QUERY_TILE = 128     # tokens per query tile of the tensor-memory attention kernel
 
 
 class StepError(ValueError):
@@ -48,6 +45,15 @@ def _align4(n):
     return (n + 3) & ~3
 
 
+@dataclass
+class _Description:
+    """A step as it is uploaded: one int32 vector, where its sections lie, and the host's view."""
+    packed: np.ndarray
+    offsets: dict            # section name -> (first int, count); planners' sections are "key.name"
+    segments: Segments
+    max_context: int
+
+
 class StepRunner:
     def __init__(self, model, cache, *, max_step_tokens=4096, use_graphs=True, graph_max_batch=256):
         self.model, self.cache = model, cache
@@ -55,6 +61,8 @@ class StepRunner:
         self.views = cache.views(model.order)
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and model.is_graph_safe()
         self.graph_max_batch = graph_max_batch
+        planners = model.step_planners() if hasattr(model, "step_planners") else {}
+        self.planners = [planners[key] for key in sorted(planners)]
         self._capacity = 0
         self._meta_dev = None
         self._ring = PinnedRing() if self.device.type == "cuda" else None
@@ -102,80 +110,74 @@ class StepRunner:
             if any(type(w) is not int or not 0 <= w < len(tokens) for w in entry.want):
                 raise StepError(f"request {entry.request_id!r}: wanted places must index its tokens of this step")
 
-    def _describe_single_tokens(self, entries):
-        """The description of a step in which every request brings one token.  Consecutive decode steps
-        of the same requests differ only in the tokens and the positions: the packed vector of the last
-        such step is kept and those entries are overwritten."""
-        key = tuple((e.request_id, tuple(e.want), e.feed) for e in entries)
-        starts = np.fromiter((self.cache.written(e.request_id) for e in entries), dtype=np.int64, count=len(entries))
-        kept = self._single_token_template
-        if kept is None or kept[0] != key:
-            packed, offsets, host, n, s, _ = self._describe_general(entries)
-            self._single_token_template = kept = (key, packed, offsets, host)
-        _, packed, offsets, host = kept
-        n = len(entries)
-        begin = offsets["token_ids"][0]
-        packed[begin:begin + n] = [e.tokens[0] for e in entries]
-        for name in ("positions", "seg_pos0"):
-            begin = offsets[name][0]
-            packed[begin:begin + n] = starts
-        longest = int(starts.max()) + 1
-        begin = offsets["decode_info"][0]
-        packed[begin + 1:begin + 4 * n:4] = starts
-        packed[begin + 3:begin + 4 * n:4] = longest
-        host = dict(host, seg_pos0=starts)
-        return packed, offsets, host, n, n, longest
-
-    def _describe(self, entries):
+    def _describe(self, entries) -> _Description:
         """Host arrays of the batch, packed into one int32 vector with section offsets."""
         if all(len(e.tokens) == 1 for e in entries):
             return self._describe_single_tokens(entries)
         return self._describe_general(entries)
 
-    def _describe_general(self, entries):
+    def _describe_single_tokens(self, entries) -> _Description:
+        """The description of a step in which every request brings one token.  Consecutive decode steps
+        of the same requests differ only in the tokens and the positions: the packed vector of the last
+        such step is kept and those entries are overwritten.
+
+        What is kept holds block-table rows, so the rows are part of the key: a request id that was
+        released and admitted again sits in another row, and the step must be described anew.
+        """
+        cache = self.cache
+        key = tuple((e.request_id, cache.row(e.request_id), tuple(e.want), e.feed) for e in entries)
+        kept = self._single_token_template
+        if kept is None or kept[0] != key:
+            description = self._describe_general(entries)
+            self._single_token_template = (key, description)
+            return description
+        description = kept[1]
+        packed, offsets, segments = description.packed, description.offsets, description.segments
+        n = len(entries)
+        starts = np.fromiter((cache.written(e.request_id) for e in entries), dtype=np.int64, count=n)
+        begin = offsets["token_ids"][0]
+        packed[begin:begin + n] = [e.tokens[0] for e in entries]
+        for name in ("positions", "seg_pos0"):
+            begin = offsets[name][0]
+            packed[begin:begin + n] = starts
+        segments = Segments(rows=segments.rows, first=segments.first, lens=segments.lens, starts=starts, n_tokens=n)
+        for planner in self.planners:
+            arrays = {name[len(planner.key) + 1:]: packed[begin:begin + count]
+                      for name, (begin, count) in offsets.items() if name.startswith(planner.key + ".")}
+            if not planner.refresh_single_tokens(arrays, segments):
+                description = self._describe_general(entries)
+                self._single_token_template = (key, description)
+                return description
+        description = _Description(packed, offsets, segments, int(starts.max()) + 1)
+        self._single_token_template = (key, description)
+        return description
+
+    def _describe_general(self, entries) -> _Description:
+        cache = self.cache
         lens = np.array([len(e.tokens) for e in entries], dtype=np.int64)
-        starts = np.array([self.cache.written(e.request_id) for e in entries], dtype=np.int64)
-        rows = np.array([self.cache.row(e.request_id) for e in entries], dtype=np.int64)
+        starts = np.array([cache.written(e.request_id) for e in entries], dtype=np.int64)
+        rows = np.array([cache.row(e.request_id) for e in entries], dtype=np.int64)
         n, s = int(lens.sum()), len(entries)
-        seg_start = np.zeros(s, dtype=np.int64)
-        np.cumsum(lens[:-1], out=seg_start[1:])
+        first = np.zeros(s, dtype=np.int64)
+        np.cumsum(lens[:-1], out=first[1:])
+        segments = Segments(rows=rows, first=first, lens=lens, starts=starts, n_tokens=n)
         token_ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=n)
         seg_of_token = np.repeat(np.arange(s), lens)
-        positions = np.arange(n) - seg_start[seg_of_token] + starts[seg_of_token]
+        positions = np.arange(n) - first[seg_of_token] + starts[seg_of_token]
         token_row = rows[seg_of_token]
-        logit_rows = np.array([seg_start[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int64)
-        # query tiles of segments longer than one token: (first token, its position, rows, block-table row)
-        tiles = [(seg_start[i] + off, starts[i] + off, min(QUERY_TILE, int(lens[i]) - off), rows[i])
-                 for i in np.nonzero(lens > 1)[0] for off in range(0, int(lens[i]), QUERY_TILE)]
-        # the longest tiles of the longest contexts first: they take longest, the short ones fill the gaps
-        tiles.sort(key=lambda t: -(t[1] + t[2]))
-        tile_info = np.array(tiles, dtype=np.int64).reshape(-1)
-        # the same tokens cut for kernels that take whole tiles of 128 tokens: those tiles, and 64-token
-        # tiles for what they leave over (short segments and the tails of long ones)
-        big, rest = [], []
-        for i in np.nonzero(lens > 1)[0]:
-            whole = int(lens[i]) // BIG_QUERY_TILE * BIG_QUERY_TILE
-            big += [(seg_start[i] + off, starts[i] + off, BIG_QUERY_TILE, rows[i]) for off in range(0, whole, BIG_QUERY_TILE)]
-            rest += [(seg_start[i] + off, starts[i] + off, min(QUERY_TILE, int(lens[i]) - off), rows[i])
-                     for off in range(whole, int(lens[i]), QUERY_TILE)]
-        big.sort(key=lambda t: -(t[1] + t[2]))
-        rest.sort(key=lambda t: -(t[1] + t[2]))
-        big_tile_info = np.array(big, dtype=np.int64).reshape(-1)
-        rest_tile_info = np.array(rest, dtype=np.int64).reshape(-1)
-        # single-token segments: (token, its position, block-table row, the longest context among them)
-        single = np.nonzero(lens == 1)[0]
-        decode_info = np.stack([seg_start[single], starts[single], rows[single],
-                                np.full_like(single, int(starts[single].max()) + 1)],
-                               axis=1).reshape(-1) if len(single) else np.zeros(0, dtype=np.int64)
+        logit_rows = np.array([first[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int64)
         # places of tokens that are still on the device: (index in the flat batch, index in the source buffer)
         feed = np.array([v for i, e in enumerate(entries) if e.feed is not None
-                         for v in (seg_start[i] + lens[i] - 1, e.feed)], dtype=np.int64)
+                         for v in (first[i] + lens[i] - 1, e.feed)], dtype=np.int64)
+        sections = [("token_ids", token_ids), ("positions", positions), ("token_row", token_row),
+                    ("seg_row", rows), ("seg_start", first), ("seg_len", lens), ("seg_pos0", starts),
+                    ("logit_rows", logit_rows)]
+        for planner in self.planners:
+            for name, values in planner.plan(segments).items():
+                sections.append((f"{planner.key}.{name}", np.asarray(values).reshape(-1)))
         # "feed" comes last: recorded graphs hold the offsets of the sections before it, which for a step of
         # single tokens depend on the number of requests only
-        sections = [("token_ids", token_ids), ("positions", positions), ("token_row", token_row),
-                    ("seg_row", rows), ("seg_start", seg_start), ("seg_len", lens), ("seg_pos0", starts),
-                    ("logit_rows", logit_rows), ("tile_info", tile_info), ("decode_info", decode_info),
-                    ("big_tile_info", big_tile_info), ("rest_tile_info", rest_tile_info), ("feed", feed)]
+        sections.append(("feed", feed))
         offsets, total = {}, 0
         for name, values in sections:
             offsets[name] = (total, len(values))
@@ -184,23 +186,30 @@ class StepRunner:
         for name, values in sections:
             begin, count = offsets[name]
             packed[begin:begin + count] = values
-        host = dict(seg_row=rows, seg_start=seg_start, seg_len=lens, seg_pos0=starts)
-        return packed, offsets, host, n, s, int((starts + lens).max())
+        return _Description(packed, offsets, segments, int((starts + lens).max()))
 
-    def _context(self, offsets, host, n, s, max_context, min_context=0):
+    def _context(self, description, max_context=None, min_context=0):
+        offsets, segments = description.offsets, description.segments
+
         def section(name):
             begin, count = offsets[name]
             return self._meta_dev[begin:begin + count]
+
+        plans = {}
+        for planner in self.planners:
+            view = plans[planner.key] = PlanView()
+            for name, (begin, count) in offsets.items():
+                if name.startswith(planner.key + "."):
+                    short = name[len(planner.key) + 1:]
+                    view.array[short], view.count[short] = self._meta_dev[begin:begin + count], count
         return StepContext(
-            n_tokens=n, n_segments=s, dtype=self.model.dtype, device=self.device,
+            n_tokens=segments.n_tokens, n_segments=segments.n_segments, dtype=self.model.dtype, device=self.device,
             token_ids=section("token_ids"), positions=section("positions"), token_row=section("token_row"),
             seg_row=section("seg_row"), seg_start=section("seg_start"), seg_len=section("seg_len"),
-            seg_pos0=section("seg_pos0"), n_tiles=offsets["tile_info"][1] // 4, tile_info=section("tile_info"),
-            n_decode=offsets["decode_info"][1] // 4, decode_info=section("decode_info"),
-            n_big_tiles=offsets["big_tile_info"][1] // 4, big_tile_info=section("big_tile_info"),
-            n_rest_tiles=offsets["rest_tile_info"][1] // 4, rest_tile_info=section("rest_tile_info"),
-            max_context=max_context, min_context=min_context, h_seg_row=host["seg_row"], h_seg_start=host["seg_start"],
-            h_seg_len=host["seg_len"], h_seg_pos0=host["seg_pos0"], extras=self._extras)
+            seg_pos0=section("seg_pos0"), plans=plans,
+            max_context=description.max_context if max_context is None else max_context, min_context=min_context,
+            h_seg_row=segments.rows, h_seg_start=segments.first, h_seg_len=segments.lens,
+            h_seg_pos0=segments.starts, extras=self._extras)
 
     def _upload(self, packed):
         self._reserve(len(packed))
@@ -226,9 +235,10 @@ class StepRunner:
         self._validate(entries)
         for entry in entries:
             self.cache.ensure(entry.request_id, self.cache.written(entry.request_id) + len(entry.tokens))
-        packed, offsets, host, n, s, max_context = self._describe(entries)
+        description = self._describe(entries)
+        offsets, n = description.offsets, description.segments.n_tokens
         self.cache.flush_tables()
-        self._upload(packed)
+        self._upload(description.packed)
         feed_begin, feed_count = offsets["feed"]
         if feed_count:
             if token_source is None:
@@ -236,12 +246,11 @@ class StepRunner:
             begin = offsets["token_ids"][0]
             ops.feed_tokens(self._meta_dev[begin:begin + n], self._meta_dev[feed_begin:feed_begin + feed_count],
                             feed_count // 2, token_source)
-        all_single = offsets["tile_info"][1] == 0 and offsets["logit_rows"][1] == n \
-            and all(e.want == [0] for e in entries)
+        all_single = all(len(e.tokens) == 1 and e.want == [0] for e in entries)
         if self.use_graphs and all_single and n <= self.graph_max_batch:
-            logits = self._run_graph(offsets, host, n, s, max_context)
+            logits = self._run_graph(description)
         else:
-            ctx = self._context(offsets, host, n, s, max_context)
+            ctx = self._context(description)
             begin, count = offsets["logit_rows"]
             before = ops.launch_count()
             logits = self.model.forward(ctx, self.views, self._meta_dev[begin:begin + count] if count else None)
@@ -251,32 +260,44 @@ class StepRunner:
         self.steps_run += 1
         return logits
 
-    def _run_graph(self, offsets, host, n, s, max_context):
-        """Replay (after recording, the first time) the graphs of an all-single-token step.
+    def check(self, wait=True) -> None:
+        """Raise if a kernel of an earlier step reported a fault of its own (a bounded wait that ran
+        out).  Kernels with such reports register them with ``ops.register_post_step_check``.  A check
+        costs nothing unless its kernel was launched since the last one; then it waits for the device,
+        or with ``wait=False`` reports a step or two late instead (``ops.ErrorWord``)."""
+        ops.run_post_step_checks(wait)
+
+    def _run_graph(self, description):
+        """Replay the graphs of an all-single-token step; the first step of its kind records them.
 
         A step is recorded as a chain of graphs, a few layers each, not as one: submitting a graph of
         several hundred kernels takes the host most of a millisecond before the GPU sees any of it,
         and a step cannot be submitted before the previous one's tokens are known.  With a chain the
         GPU runs the first layers while the host submits the rest.
+
+        The recording step runs the model once, eagerly, outside the recording (libraries set up their
+        workspaces then) and returns that run's logits; it is not replayed as well, so a part that
+        updates memory in place advances once per step here too.
         """
+        n = description.segments.n_tokens
         bucket = 512
-        while bucket < max_context:
+        while bucket < description.max_context:
             bucket *= 2
         key = (n, bucket)
         record = self._graphs.get(key)
         if record is None:
-            ctx = self._context(offsets, host, n, s, bucket, min_context=bucket // 2 + 1 if bucket > 512 else 1)
-            begin, count = offsets["logit_rows"]
+            ctx = self._context(description, bucket, min_context=bucket // 2 + 1 if bucket > 512 else 1)
+            begin, count = description.offsets["logit_rows"]
             logit_rows = self._meta_dev[begin:begin + count]
-            # one eager run first: libraries set up their workspaces outside the recording
-            self.model.forward(ctx, self.views, logit_rows)
+            before = ops.launch_count()
+            eager_logits = self.model.forward(ctx, self.views, logit_rows)
+            launches = ops.launch_count() - before
             torch.cuda.synchronize()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             graphs = []
             stream = torch.cuda.Stream()
             stream.wait_stream(torch.cuda.current_stream())
-            before = ops.launch_count()
             with torch.cuda.stream(stream):
                 current = torch.cuda.CUDAGraph()
                 current.capture_begin(pool=self._graph_pool)
@@ -295,9 +316,10 @@ class StepRunner:
                 graphs.append(current)
             torch.cuda.current_stream().wait_stream(stream)
             # the graphs hold addresses of what the parts keep in ``extras`` (scratch): keep those alive
-            record = (graphs, logits, ops.launch_count() - before, dict(self._extras))
-            self._graphs[key] = record
-            self.launches_per_graph[n] = record[2]
+            self._graphs[key] = (graphs, logits, launches, dict(self._extras))
+            self.launches_per_graph[n] = launches
+            self.kernel_launches += launches
+            return eager_logits
         graphs, logits, launches = record[:3]
         for graph in graphs:
             graph.replay()

@@ -10,6 +10,7 @@ from __future__ import annotations
 import functools
 from ctypes import c_float, c_int, c_void_p
 
+import numpy as np
 import torch
 
 from . import attention_tc, build
@@ -18,6 +19,59 @@ from .ops import KernelError, _check, _p, _stream
 _libs: dict = {}
 KV_TILE = 64
 MAX_DECODE_SPAN = 8192
+QUERY_TILE = 64          # tokens per query tile of ``attn_prefill_kernel``
+BIG_QUERY_TILE = attention_tc.TILE     # tokens per query tile of the tensor-memory kernel
+
+
+PLAN_KEY = "paged_attention"     # the step planner whose arrays ``attend`` reads (``describe_segments`` makes them)
+
+
+def describe_segments(first, starts, lens, rows) -> dict:
+    """A step's segments as the attention kernels of this module and of ``attention_tc`` want them
+    (numpy int64 arrays in, one entry per segment: first token in the flat batch, its absolute
+    position, tokens, block-table row).
+
+    ``tile_info``       query tiles of 64 tokens of every segment longer than one token; four ints a
+                        tile: (first token in the flat batch, its absolute position, tokens in the tile,
+                        block-table row)
+    ``big_tile_info``   the same segments' whole tiles of 128 tokens (for the tensor-memory kernel) ...
+    ``rest_tile_info``  ... and 64-token tiles of what those leave over (short segments, tails)
+    ``decode_info``     segments of exactly one token: (token, its position, block-table row, the longest
+                        context among these segments)
+
+    Tiles are sorted with the longest contexts first: they take longest, the short ones fill the gaps.
+    """
+    def tiles(indices, tile, begin_of=lambda length: 0, end_of=lambda length: length):
+        found = [(first[i] + off, starts[i] + off, min(tile, end_of(int(lens[i])) - off), rows[i])
+                 for i in indices for off in range(begin_of(int(lens[i])), end_of(int(lens[i])), tile)]
+        found.sort(key=lambda t: -(t[1] + t[2]))
+        return np.array(found, dtype=np.int64).reshape(-1)
+
+    multi = np.nonzero(lens > 1)[0]
+    whole = lambda length: length // BIG_QUERY_TILE * BIG_QUERY_TILE
+    single = np.nonzero(lens == 1)[0]
+    if len(single):
+        decode_info = np.stack([first[single], starts[single], rows[single],
+                                np.full_like(single, int(starts[single].max()) + 1)], axis=1).reshape(-1)
+    else:
+        decode_info = np.zeros(0, dtype=np.int64)
+    return dict(tile_info=tiles(multi, QUERY_TILE), big_tile_info=tiles(multi, BIG_QUERY_TILE, end_of=whole),
+                rest_tile_info=tiles(multi, QUERY_TILE, begin_of=whole), decode_info=decode_info)
+
+
+def refresh_single_tokens(arrays, starts) -> None:
+    """``describe_segments`` of a step of single tokens whose rows are those of the step before:
+    only the positions change (``arrays``: numpy views of the arrays made then, edited in place)."""
+    info = arrays["decode_info"]
+    n = len(starts)
+    info[1:4 * n:4] = starts
+    info[3:4 * n:4] = int(starts.max()) + 1
+
+
+def step_plan(ctx):
+    """The planner's arrays for the step in flight: (device arrays, their lengths)."""
+    view = ctx.plans[PLAN_KEY]
+    return view.array, view.count
 
 
 def supports(head_dim, n_q_heads, n_kv_heads) -> bool:
@@ -144,7 +198,7 @@ def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_
 def projection_tail_usable(ctx, qkv, cache, n_q_heads, n_kv_heads, head_dim, rotary_dim, norm_weights) -> bool:
     """Can the single-token kernel take the projection's raw output (``attend_projection``)?  Every token of
     the step a single token of its request, bfloat16 throughout, at most 16 query heads per kv head."""
-    return (ctx.n_decode == ctx.n_tokens and ctx.n_tiles == 0 and qkv.dtype == torch.bfloat16
+    return (step_plan(ctx)[1]["decode_info"] == 4 * ctx.n_tokens and qkv.dtype == torch.bfloat16
             and cache.pages.dtype == torch.bfloat16 and supports(head_dim, n_q_heads, n_kv_heads)
             and n_q_heads // n_kv_heads <= 16 and rotary_dim % 4 == 0 and rotary_dim <= head_dim
             and all(w is None or w.dtype == torch.bfloat16 for w in norm_weights))
@@ -166,12 +220,14 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
         raise KernelError("attention: the rotary table must be float32 [positions, rotary_dim]")
     # the kernels cut the step's own longest context (decode_info carries it) into n_spans spans; ctx.max_context
     # may be a recorded graph's upper bound, ctx.min_context its lower one
-    n_spans, longest_span = plan_spans(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
+    arrays, counts = step_plan(ctx)
+    n_decode = counts["decode_info"] // 4
+    n_spans, longest_span = plan_spans(n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
                                        getattr(ctx, "min_context", 0) or None)
-    part_o, part_ml = decode_scratch(ctx, ctx.n_decode, n_q_heads, n_spans, head_dim)
+    part_o, part_ml = decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim)
     lib = library(head_dim)
     _check(lib, lib.qil_attn_decode_qkv(
-        _p(qkv), _p(cache.pages), _p(out), _p(ctx.decode_info), c_int(ctx.n_decode), _p(part_o), _p(part_ml),
+        _p(qkv), _p(cache.pages), _p(out), _p(arrays["decode_info"]), c_int(n_decode), _p(part_o), _p(part_ml),
         c_int(n_spans), c_int(-longest_span), _p(cache.block_table), c_int(cache.block_table.shape[1]),
         c_int(n_q_heads), c_int(n_kv_heads), c_int(own_kv_heads), c_int(cache.page_size),
         c_int(cache.pages.shape[0]), c_int(window), c_float(scale), _p(q_norm), _p(k_norm), c_float(float(eps)),
@@ -186,19 +242,22 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
         raise KernelError("the tensor-core attention takes bfloat16 queries and pages")
     if tuple(cache.pages.shape[1:]) != (2, n_kv_heads, cache.page_size, head_dim):
         raise KernelError(f"attention: cache layout {tuple(cache.pages.shape)}")
-    if ctx.n_big_tiles and attention_tc.supports(head_dim, cache.page_size, window):
+    arrays, counts = step_plan(ctx)
+    n_tiles, n_big, n_rest, n_decode = (counts[name] // 4 for name in
+                                        ("tile_info", "big_tile_info", "rest_tile_info", "decode_info"))
+    if n_big and attention_tc.supports(head_dim, cache.page_size, window):
         # whole 128-token tiles on tcgen05 with the accumulators in tensor memory, the leftovers below
-        attention_tc.prefill(q, cache.pages, out, ctx.big_tile_info, ctx.n_big_tiles, cache.block_table,
+        attention_tc.prefill(q, cache.pages, out, arrays["big_tile_info"], n_big, cache.block_table,
                              n_q_heads, n_kv_heads, cache.page_size, scale)
-        if ctx.n_rest_tiles:
-            prefill(q, cache.pages, out, ctx.rest_tile_info, ctx.n_rest_tiles, cache.block_table, n_q_heads,
+        if n_rest:
+            prefill(q, cache.pages, out, arrays["rest_tile_info"], n_rest, cache.block_table, n_q_heads,
                     n_kv_heads, head_dim, cache.page_size, window, scale)
-    elif ctx.n_tiles:
-        prefill(q, cache.pages, out, ctx.tile_info, ctx.n_tiles, cache.block_table, n_q_heads, n_kv_heads,
+    elif n_tiles:
+        prefill(q, cache.pages, out, arrays["tile_info"], n_tiles, cache.block_table, n_q_heads, n_kv_heads,
                 head_dim, cache.page_size, window, scale)
-    if ctx.n_decode:
-        n_spans, longest_span = plan_spans(ctx.n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
+    if n_decode:
+        n_spans, longest_span = plan_spans(n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
                                            getattr(ctx, "min_context", 0) or None)
-        part_o, part_ml = decode_scratch(ctx, ctx.n_decode, n_q_heads, n_spans, head_dim)
-        decode(q, cache.pages, out, ctx.decode_info, ctx.n_decode, part_o, part_ml, n_spans, -longest_span,
+        part_o, part_ml = decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim)
+        decode(q, cache.pages, out, arrays["decode_info"], n_decode, part_o, part_ml, n_spans, -longest_span,
                cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale)

@@ -10,18 +10,21 @@ from ctypes import c_float, c_int
 import torch
 
 from . import build
+from . import ops
 from .ops import KernelError, _check, _need, _p, _stream
 
 HEAD_DIM = 128
 TILE = 128
 _lib = None
-_error_word = None
+_fault = ops.ErrorWord(lambda code: f"attention_tc: a wait inside the kernel ran out (code {code}: 1x producer, "
+                                    f"13-17 MMA issuer, 2x softmax warps)")
 
 
 def library():
     global _lib
     if _lib is None:
         _lib = build.load("qil_attn_tc", ["attention_tc.cu"])
+        ops.register_post_step_check(check)
         if _lib.qil_attn_tc_head_dim() != HEAD_DIM:
             raise KernelError("attention_tc was built for another head size")
     return _lib
@@ -35,25 +38,18 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
             lib=None):
     """q, out bfloat16 [N, Hq*128]; pages [num_pages, 2, Hkv, page_size, 128];
     tile_info int32 [n_tiles * 4] = (first token, its position, 128, block-table row)."""
-    global _error_word
     _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2); _need(pages, "pages", torch.bfloat16, 5)
     if tuple(pages.shape[1:]) != (2, n_kv_heads, page_size, HEAD_DIM) or q.shape[1] != n_q_heads * HEAD_DIM:
         raise KernelError("attention_tc: shapes do not match the head counts")
-    if _error_word is None:
-        _error_word = torch.zeros(1, dtype=torch.int32, device=q.device)
     lib = lib or library()
+    word = _fault.tensor(q.device)
+    _fault.mark()
     _check(lib, lib.qil_attn_tc_prefill(
         _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), c_int(q.shape[0]), _p(block_table),
         c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]),
-        c_float(scale), _p(_error_word), _p(trace), _stream()), "attention (128-token tiles)")
+        c_float(scale), _p(word), _p(trace), _stream()), "attention (128-token tiles)")
 
 
-def check() -> None:
-    """Raise if a bounded wait inside an earlier launch ran out (synchronises the device)."""
-    if _error_word is None:
-        return
-    code = int(_error_word.item())
-    if code:
-        _error_word.zero_()
-        raise KernelError(f"attention_tc: a wait inside the kernel ran out (code {code}: 1x producer, "
-                          f"13-17 MMA issuer, 2x softmax warps)")
+def check(wait=True) -> None:
+    """Raise if a bounded wait inside a launch ran out (see ``ops.ErrorWord.check``)."""
+    _fault.check(wait)

@@ -11,27 +11,39 @@ from ctypes import c_float, c_int, c_void_p
 import torch
 
 from . import build
+from . import ops
 from .ops import KernelError, _check, _need, _p, _stream
 
 _lib = None
-_error_word = None
 _sm_count = None
 MIN_ROWS = 17
+
+
+def _describe_fault(code):
+    where = {1: "producer waiting for a free stage", 2: "producer draining its copies",
+             3: "MMA issuer waiting for a free accumulator", 4: "MMA issuer waiting for a stage's data",
+             5: "epilogue waiting for the accumulator"}.get(code, "unknown place")
+    return f"gemm_tc: a wait inside the kernel ran out ({where}, code {code})"
+
+
+_fault = ops.ErrorWord(_describe_fault)
 
 
 def library():
     global _lib
     if _lib is None:
         _lib = build.load("qil_gemm_tc", ["gemm_tc.cu"])
+        ops.register_post_step_check(check)
     return _lib
 
 
 def error_word(device):
-    global _error_word, _sm_count
-    if _error_word is None:
-        _error_word = torch.zeros(1, dtype=torch.int32, device=device)
+    """The kernels' error word, marked as possibly written: call right before a launch."""
+    global _sm_count
+    if _sm_count is None:
         _sm_count = torch.cuda.get_device_properties(device).multi_processor_count
-    return _error_word
+    _fault.mark()
+    return _fault.tensor(device)
 
 
 def usable(a, weight) -> bool:
@@ -121,14 +133,6 @@ def gemm_tc_qkv(a, weight, bias, q_out, pages, rope_table, q_norm, k_norm, eps, 
     return q_out
 
 
-def check() -> None:
-    """Raise if a bounded wait inside any earlier gemm_tc launch ran out (synchronises the device)."""
-    if _error_word is None:
-        return
-    code = int(_error_word.item())
-    if code:
-        _error_word.zero_()
-        where = {1: "producer waiting for a free stage", 2: "producer draining its copies",
-                 3: "MMA issuer waiting for a free accumulator", 4: "MMA issuer waiting for a stage's data",
-                 5: "epilogue waiting for the accumulator"}.get(code, "unknown place")
-        raise KernelError(f"gemm_tc: a wait inside the kernel ran out ({where}, code {code})")
+def check(wait=True) -> None:
+    """Raise if a bounded wait inside a gemm_tc launch ran out (see ``ops.ErrorWord.check``)."""
+    _fault.check(wait)

@@ -41,6 +41,69 @@ def dtype_code(dtype) -> int:
         raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
 
 
+_post_step_checks: list = []
+
+
+def register_post_step_check(check) -> None:
+    """``check()`` raises if a kernel reported a fault of its own since the last call.  A kernel whose
+    waits are bounded reports through an error word; its module registers the reader of that word here
+    when its library is first loaded, and the step function's owner calls them after steps."""
+    if check not in _post_step_checks:
+        _post_step_checks.append(check)
+
+
+def run_post_step_checks(wait=True) -> None:
+    for check in _post_step_checks:
+        check(wait)
+
+
+class ErrorWord:
+    """An int32 on the device that kernels with bounded waits set when a wait runs out, and its reader.
+
+    ``check(wait=True)`` reads the word if a kernel that may set it was launched since the last check
+    (``mark``); that waits for the device.  ``check(wait=False)`` never waits: it queues a copy of the
+    word to pinned memory behind the work queued so far and reports what an earlier such copy
+    brought, so a fault is reported a step or two late but the host never stalls a stream it is
+    running ahead of.  The word stays set until it has been reported.
+    """
+
+    def __init__(self, describe):
+        self._describe = describe
+        self._word = self._host = self._event = None
+        self._launched = self._copy_queued = False
+
+    def tensor(self, device):
+        if self._word is None:
+            self._word = torch.zeros(1, dtype=torch.int32, device=device)
+            self._host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+            self._event = torch.cuda.Event()
+        return self._word
+
+    def mark(self) -> None:
+        self._launched = True
+
+    def check(self, wait=True) -> None:
+        if self._word is None:
+            return
+        code = 0
+        if self._copy_queued and (wait or self._event.query()):
+            self._event.synchronize()
+            self._copy_queued = False
+            code = int(self._host[0])
+        if self._launched:
+            self._launched = False
+            if wait:
+                code = code or int(self._word.item())
+            else:
+                self._host.copy_(self._word, non_blocking=True)
+                self._event.record()
+                self._copy_queued = True
+        if code:
+            self._word.zero_()
+            self._copy_queued = False
+            raise KernelError(self._describe(code))
+
+
 _launches = 0
 
 
@@ -84,6 +147,17 @@ def embed_gather(table, ids, out):
     _check(lib, lib.qil_embed_gather(_p(table), c_int(dtype_code(table.dtype)), _p(ids), _p(out),
                                      c_int(dtype_code(out.dtype)), c_int(ids.shape[0]), c_int(table.shape[1]),
                                      c_int(table.shape[0]), _stream()), "embed_gather")
+    return out
+
+
+def fill_normal(out, seed, std, mean=0.0):
+    """out[i] = mean + std * z(seed, i), z close to N(0, 1) from a counter hash (the same bits as
+    ``weights.random_init.normal_values`` gives on the host)."""
+    _need(out, "out")
+    lib = core()
+    _check(lib, lib.qil_fill_normal(_p(out), c_int(dtype_code(out.dtype)), c_longlong(out.numel()),
+                                    ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), c_float(std), c_float(mean),
+                                    _stream()), "fill_normal")
     return out
 
 

@@ -35,11 +35,13 @@ def require_gpu(device) -> torch.device:
     return device
 
 
-def load_model(directory, *, device="cuda", dtype=torch.bfloat16):
+def load_model(directory, *, device="cuda", dtype=torch.bfloat16, keep_stored_32bit=False):
+    """``keep_stored_32bit``: in a bfloat16 run, leave tensors that the folder stores in 32 bits as they
+    are instead of casting them (``weights.loader``)."""
     device, dtype = require_gpu(device), resolve_dtype(dtype)
     entry, config = registry.read_model_config(directory)
     model = entry.build(config)
-    load_weights(model, directory, device=device, dtype=dtype)
+    load_weights(model, directory, device=device, dtype=dtype, keep_stored_32bit=keep_stored_32bit)
     return model
 
 

@@ -1,6 +1,6 @@
 """Model parts: each owns its sizes, constants and parameters, none knows its model."""
-from .base import (FeedForward, KVCacheSpec, Mixer, Norm, Param, Part, PositionEncoding,
-                   StateSpec, StepContext)
+from .base import (FeedForward, KVCacheSpec, Mixer, Norm, Param, Part, PlanView, PositionEncoding, Segments,
+                   StateSpec, StepContext, StepPlanner)
 from .linear import Linear, StackedLinear
 from .norm import RMSNorm
 from .rotary import RotaryEmbedding, rotary_table

@@ -13,8 +13,25 @@ from __future__ import annotations
 import torch
 
 from ..kernels import attention_mma, gemm_tc, ops
-from .base import KVCacheSpec, Mixer, Param
+from .base import KVCacheSpec, Mixer, Param, StepPlanner
 from .linear import Linear, StackedLinear
+
+
+class PagedAttentionPlanner(StepPlanner):
+    """The host hook of the attention mixers: a step's segments cut into the query tiles and the list
+    of single tokens that the attention kernels take (``attention_mma.describe_segments``).  All
+    attention layers of a model share the one plan."""
+    key = attention_mma.PLAN_KEY
+
+    def plan(self, segments):
+        return attention_mma.describe_segments(segments.first, segments.starts, segments.lens, segments.rows)
+
+    def refresh_single_tokens(self, arrays, segments):
+        attention_mma.refresh_single_tokens(arrays, segments.starts)
+        return True
+
+
+_PLANNER = PagedAttentionPlanner()
 
 
 class GroupedQueryAttention(Mixer):
@@ -65,6 +82,9 @@ class GroupedQueryAttention(Mixer):
         super().finalize(device, dtype)
         if self.q_norm is not None and self.q_norm.data.dtype != self.k_norm.data.dtype:
             self.q_norm.data, self.k_norm.data = self.q_norm.data.float(), self.k_norm.data.float()
+
+    def step_planners(self):
+        return {**super().step_planners(), _PLANNER.key: _PLANNER}
 
     def cache_spec(self):
         if self.reads_shared_cache:

@@ -20,6 +20,9 @@ Interfaces
                 un-normed input and the norm (``norm=``) and applies it itself, so that it can
                 fuse the norm into its first product; the others get normed input.
 ``Block``       ``forward(ctx, x, cache) -> x`` (arrangement of the above).
+``StepPlanner`` what a part's kernels need to know about a step beyond its segments (query
+                tiles, work lists): computed on the host from ``Segments``, packed and uploaded by
+                the step function with everything else, handed back in ``ctx.plans[key]``.
 """
 from __future__ import annotations
 
@@ -33,15 +36,19 @@ class Param:
 
     ``init`` is ``"normal"`` (N(0, std)), ``"norm"`` (1 + N(0, std)) or ``"zeros"``.
     Several checkpoint names may point to one Param (tied embeddings).
+    ``keep_32bit``: a tensor that the checkpoint stores in 32 bits stays so in a bfloat16 run (for
+    parameters whose part computes in float32, such as router weights or decay rates); all others
+    are cast to the run's dtype when they are loaded, as the reference does (qil/model.py:197).
     """
 
-    __slots__ = ("shape", "init", "std", "data", "integer")
+    __slots__ = ("shape", "init", "std", "data", "integer", "keep_32bit")
 
-    def __init__(self, shape, init="normal", std=0.02, integer=False):
+    def __init__(self, shape, init="normal", std=0.02, integer=False, keep_32bit=False):
         self.shape = tuple(int(n) for n in shape)
         self.init = init
         self.std = std
         self.integer = integer
+        self.keep_32bit = keep_32bit
         self.data: torch.Tensor | None = None
 
     def __repr__(self):
@@ -99,6 +106,14 @@ class Part:
     def is_graph_safe(self) -> bool:
         return self.graph_safe and all(child.is_graph_safe() for child in self.children())
 
+    def step_planners(self) -> dict:
+        """key -> StepPlanner for this part and its children.  Parts that give the same key share one
+        plan per step (all attention layers of a model read the same query tiles)."""
+        result = {}
+        for child in self.children():
+            result.update(child.step_planners())
+        return result
+
 
 class Norm(Part):
     def forward(self, ctx, x, rows=None):
@@ -129,6 +144,55 @@ class FeedForward(Part):
 
 
 @dataclass
+class Segments:
+    """The batch of one step as the host sees it (numpy int64 arrays, one entry per segment).
+
+    A segment is one request's run of consecutive tokens in the flat batch.  This is all the
+    step function knows about a batch; whatever else a kernel wants (tiles of its own size, lists
+    of single tokens) a ``StepPlanner`` derives from it.
+    """
+    rows: object        # [S] request row (block-table row, state slot)
+    first: object       # [S] index of the segment's first token in the flat batch
+    lens: object        # [S] tokens in the segment
+    starts: object      # [S] absolute position of the segment's first token
+    n_tokens: int
+
+    @property
+    def n_segments(self) -> int:
+        return len(self.lens)
+
+
+class StepPlanner:
+    """Host-side planning of a step for one family of kernels.
+
+    ``plan`` returns named integer arrays; the step function packs them (as int32) into the step's
+    one upload and gives the part device views of them: ``ctx.plans[key].array[name]`` with
+    ``ctx.plans[key].count[name]`` entries.  For a step in which every segment is a single token
+    the length of every array may depend on the number of segments only, not on positions or
+    rows: such steps are recorded into CUDA graphs that are replayed with other positions.
+
+    ``refresh_single_tokens`` is optional: when consecutive steps bring one token each for the same
+    requests in the same rows, only positions change, and a planner that can overwrite just those
+    in its arrays of the previous step (numpy views, edited in place) returns True; returning
+    False makes the step function call ``plan`` again.
+    """
+    key = ""
+
+    def plan(self, segments: Segments) -> dict:
+        raise NotImplementedError
+
+    def refresh_single_tokens(self, arrays: dict, segments: Segments) -> bool:
+        return False
+
+
+@dataclass
+class PlanView:
+    """A planner's arrays as the parts see them: int32 device views and their lengths."""
+    array: dict = field(default_factory=dict)
+    count: dict = field(default_factory=dict)
+
+
+@dataclass
 class StepContext:
     """Everything a part may know about the step in flight.
 
@@ -148,23 +212,12 @@ class StepContext:
     seg_start: torch.Tensor          # [S] first token of the segment in the flat batch
     seg_len: torch.Tensor            # [S]
     seg_pos0: torch.Tensor           # [S] position of the segment's first token
-    # query tiles (64 tokens) of segments longer than one token:
-    # 4 ints each = (first token in the flat batch, its absolute position, rows in the tile, block-table row)
-    n_tiles: int
-    tile_info: torch.Tensor          # [n_tiles * 4]
-    # segments of exactly one token (decode rows): 4 ints each = (token, its position, block-table row,
-    # the longest context among these segments)
-    n_decode: int
-    decode_info: torch.Tensor        # [n_decode * 4]
     max_context: int                 # largest start+len over the batch's segments (host upper bound)
     # a recorded graph is replayed with other contexts than the step it was recorded from: max_context is then
     # the largest longest-context of those steps and min_context the smallest (0: this step only)
     min_context: int = 0
-    # the multi-token segments cut a second way: whole tiles of 128 tokens, and 64-token tiles for the rest
-    n_big_tiles: int = 0
-    big_tile_info: torch.Tensor = None    # [n_big_tiles * 4], same four ints as tile_info
-    n_rest_tiles: int = 0
-    rest_tile_info: torch.Tensor = None   # [n_rest_tiles * 4]
+    # key -> PlanView: what the model's step planners made of this step's segments
+    plans: dict = field(default_factory=dict)
     h_seg_row: object = None
     h_seg_start: object = None
     h_seg_len: object = None

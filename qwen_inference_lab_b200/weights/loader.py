@@ -7,8 +7,12 @@ shape; tied parameters that arrive under both names must be equal; every
 expected parameter must be covered.  All problems of a folder are collected and
 raised together as one :class:`WeightError`.
 
-Storage: bfloat16 tensors stay bfloat16, tensors stored in 32 bits stay 32-bit,
-float16 and float64 become bfloat16 and float32, integer tables become int32.
+Storage: every floating-point tensor is cast to the run's dtype as it is loaded, as the
+reference does (qil/model.py:197; tied tensors are compared after the cast), and integer
+tables become int32.  In a bfloat16 run a tensor that the file stores in 32 bits stays
+32-bit only where that is asked for: by its parameter (``Param.keep_32bit``, for
+parameters whose part computes in float32) or for the whole folder with
+``keep_stored_32bit=True`` (every product then runs on the slow 32-bit kernels).
 ``dtype=torch.float32`` (the true 32-bit path) widens everything to float32.
 """
 from __future__ import annotations
@@ -24,17 +28,17 @@ class WeightError(ValueError):
     """Missing, unexpected, duplicate, mis-shaped or inconsistent checkpoint tensors."""
 
 
-def storage_dtype(stored: torch.dtype, run_dtype: torch.dtype, integer: bool) -> torch.dtype:
+def storage_dtype(stored: torch.dtype, run_dtype: torch.dtype, integer: bool, keep_32bit: bool = False) -> torch.dtype:
     if integer or not stored.is_floating_point:
         return torch.int32
     if run_dtype == torch.float32:
         return torch.float32
-    if stored in (torch.float32, torch.float64):
+    if keep_32bit and stored in (torch.float32, torch.float64):
         return torch.float32
-    return torch.bfloat16
+    return run_dtype
 
 
-def load_weights(model, directory, *, device, dtype) -> None:
+def load_weights(model, directory, *, device, dtype, keep_stored_32bit=False) -> None:
     """Fill every Param of ``model`` from ``directory`` and finalize the model."""
     directory = Path(directory)
     expected = model.all_named_params()
@@ -66,7 +70,7 @@ def load_weights(model, directory, *, device, dtype) -> None:
                     mis_shaped.add(id(param))
                     continue
                 source = shard.tensor(name)
-                target = storage_dtype(source.dtype, dtype, param.integer)
+                target = storage_dtype(source.dtype, dtype, param.integer, keep_stored_32bit or param.keep_32bit)
                 value = source.to(device=device, dtype=target, copy=True)
                 if param.data is not None:
                     # a second name of the same parameter (tied weights): values must agree

@@ -29,17 +29,7 @@ def models(tmp_path_factory):
     return get
 
 
-def check_greedy(prompt, tokens, weights, cfg, dtype):
-    """The engine's tokens are the plain implementation's argmax at every step; in bfloat16 a
-    token may differ only where the plain float32 logits of the two are within rounding noise."""
-    sequence = list(prompt)
-    for token in tokens:
-        logits = plain.logits(sequence, weights, cfg)[-1]
-        best = int(logits.argmax())
-        if token != best:
-            assert dtype == torch.bfloat16 and float(logits[best] - logits[token]) < 0.02, \
-                f"token {token} instead of {best} after {len(sequence)} tokens"
-        sequence.append(token)
+check_greedy = harness.check_greedy
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])

@@ -310,7 +310,10 @@ def test_attention_single_tokens_from_the_projection(n_q, n_kv, d, lengths, page
         pages_b = pool.cuda().clone()
         out_b = torch.full((n, n_q * d), float("nan"), dtype=torch.bfloat16).cuda()
         part_o, part_ml = scratch()
-        ctx = SimpleNamespace(n_tokens=n, n_decode=n, n_tiles=0, max_context=bound, min_context=longest, decode_info=decode_info,
+        plan = SimpleNamespace(array=dict(decode_info=decode_info),
+                               count=dict(decode_info=4 * n, tile_info=0, big_tile_info=0, rest_tile_info=0))
+        ctx = SimpleNamespace(n_tokens=n, max_context=bound, min_context=longest,
+                              plans={attention_mma.PLAN_KEY: plan},
                               extras={"attn_decode_scratch": (part_o, part_ml)}, device=qkv.device)
         cache = SimpleNamespace(pages=pages_b, block_table=table.cuda(), page_size=page)
         assert attention_mma.projection_tail_usable(ctx, qkv, cache, n_q, n_kv, d, rotary, (q_norm, k_norm))

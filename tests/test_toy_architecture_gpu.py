@@ -1,7 +1,9 @@
 """An architecture defined here, in the test: registered, built, loaded and stepped with no change
 to the framework's files.  It is a toy, not anyone's model.  Its layers differ in kind:
 
-  0  a mixer with a state of its own (a decaying running sum kept in a per-request slot)
+  0  a mixer with a state of its own (a decaying running sum kept in a per-request slot) that walks a step's
+     tokens in chunks of 24, cut by a step planner of its own: the step function packs and uploads what the
+     planner returns without knowing what a chunk is
   1  full attention with q/k norms and full rotation
   2  attention with a window of 20 positions and a position encoding of the test's own: half of each head is
      rotated, by angles of positions squeezed by a factor plus a phase per frequency; its feed-forward is
@@ -59,8 +61,24 @@ def squeezed_angles(positions, rotary_dim, theta, squeeze):
     return positions.float()[:, None] / squeeze * inv_freq[None, :] + 0.1 * torch.arange(rotary_dim // 2).float()
 
 
+SCAN_CHUNK = 24
+
+
 def make_parts():
-    from qwen_inference_lab_b200.parts import FeedForward, Mixer, Param, PositionEncoding, StateSpec
+    import numpy as np
+    from qwen_inference_lab_b200.parts import FeedForward, Mixer, Param, PositionEncoding, StateSpec, StepPlanner
+
+    class ScanPlanner(StepPlanner):
+        """Segments cut into chunks of at most SCAN_CHUNK tokens: (first token, tokens, state slot) each."""
+        key = "toy_scan"
+
+        def plan(self, segments):
+            chunks = [(int(first) + off, min(SCAN_CHUNK, int(n) - off), int(row))
+                      for first, n, row in zip(segments.first, segments.lens, segments.rows)
+                      for off in range(0, int(n), SCAN_CHUNK)]
+            return dict(chunks=np.array(chunks, dtype=np.int64).reshape(-1))
+
+    scan_planner = ScanPlanner()
 
     class SqueezedRotation(PositionEncoding):
         """Another position encoding is another table of cosines and sines."""
@@ -79,7 +97,7 @@ def make_parts():
 
         def __init__(self, width, inner, experts, per_token, *, name):
             self.per_token, self.name = per_token, name
-            self.router = Param((experts, width), std=0.5)
+            self.router = Param((experts, width), std=0.5, keep_32bit=True)
             self.gate = [Param((inner, width), std=0.1) for _ in range(experts)]
             self.up = [Param((inner, width), std=0.1) for _ in range(experts)]
             self.down = [Param((width, inner), std=0.1) for _ in range(experts)]
@@ -119,11 +137,19 @@ def make_parts():
         def cache_spec(self):
             return StateSpec((self.state_width,), torch.float32)
 
+        def step_planners(self):
+            return {**super().step_planners(), scan_planner.key: scan_planner}
+
         def forward(self, ctx, x, cache, residual=None):
             u = x.float() @ self.w_in.data.float().t()
             h_all = torch.empty_like(u)
-            for row, start, length in zip(ctx.h_seg_row, ctx.h_seg_start, ctx.h_seg_len):
-                h = cache.slots[row]
+            plan = ctx.plans["toy_scan"]
+            assert plan.count["chunks"] == plan.array["chunks"].numel() and plan.array["chunks"].dtype == torch.int32
+            chunks = plan.array["chunks"].view(-1, 3).tolist()      # from the device: what the step function uploaded
+            assert all(0 < length <= SCAN_CHUNK for _, length, _ in chunks)
+            assert sum(length for _, length, _ in chunks) == ctx.n_tokens
+            for start, length, row in chunks:
+                h = cache.slots[row]                                 # a later chunk of a segment goes on from the slot
                 for t in range(start, start + length):
                     h = self.decay * h + u[t]
                     h_all[t] = h

@@ -71,19 +71,48 @@ def test_strict_loading_of_single_and_sharded_folders(tmp_path, cfg, seed, shard
     assert model32.layers[0].mixer.qkv._weight().dtype == torch.float32
 
 
-def test_tensors_stored_in_32_bits_stay_32_bit(tmp_path):
+def test_tensors_are_cast_to_the_run_dtype_unless_32_bits_are_asked_for(tmp_path):
+    """The reference casts every tensor as it loads it (qil/model.py:197); a folder stored in float32 must not
+    send a bfloat16 run to the 32-bit kernels behind the user's back."""
     weights = tiny_weights(TINY_A, 0, torch.bfloat16)
-    weights["model.norm.weight"] = weights["model.norm.weight"].float() + 1e-4          # not representable in bfloat16
+    exact = weights["model.norm.weight"].float() + 1e-4                                  # not representable in bfloat16
+    weights["model.norm.weight"] = exact
     weights["model.layers.0.mlp.down_proj.weight"] = weights["model.layers.0.mlp.down_proj.weight"].float()
     weights["model.layers.1.input_layernorm.weight"] = weights["model.layers.1.input_layernorm.weight"].half()
+    folder = folder_with(tmp_path, TINY_A, weights)
     model = build(TINY_A)
-    load_weights(model, folder_with(tmp_path, TINY_A, weights), device="cpu", dtype=torch.bfloat16)
+    load_weights(model, folder, device="cpu", dtype=torch.bfloat16)
+    params = model.all_named_params()
+    assert all(p.data is None or p.data.dtype == torch.bfloat16 for p in params.values())
+    assert torch.equal(params["model.norm.weight"].data, exact.to(torch.bfloat16))
+    assert model.layers[0].feed_forward.down._weight().dtype == torch.bfloat16
+    # asked for by a parameter ...
+    model = build(TINY_A)
+    model.final_norm.weight.keep_32bit = True
+    load_weights(model, folder, device="cpu", dtype=torch.bfloat16)
+    params = model.all_named_params()
+    assert params["model.norm.weight"].data.dtype == torch.float32 and torch.equal(params["model.norm.weight"].data, exact)
+    assert params["model.layers.1.input_layernorm.weight"].data.dtype == torch.bfloat16
+    assert model.layers[0].feed_forward.down._weight().dtype == torch.bfloat16
+    # ... or for the whole folder
+    model = build(TINY_A)
+    load_weights(model, folder, device="cpu", dtype=torch.bfloat16, keep_stored_32bit=True)
     params = model.all_named_params()
     assert params["model.norm.weight"].data.dtype == torch.float32
-    assert torch.equal(params["model.norm.weight"].data, weights["model.norm.weight"])
-    assert params["model.layers.0.mlp.down_proj.weight"].data.dtype == torch.float32
-    assert params["model.layers.1.input_layernorm.weight"].data.dtype == torch.bfloat16
+    assert model.layers[0].feed_forward.down._weight().dtype == torch.float32
+    assert params["model.layers.1.input_layernorm.weight"].data.dtype == torch.bfloat16       # float16 in the file
     assert params["model.embed_tokens.weight"].data.dtype == torch.bfloat16
+
+
+def test_tied_tensors_are_compared_after_the_cast(tmp_path):
+    weights = tiny_weights(TINY_A, 0, torch.bfloat16)
+    embedding = weights["model.embed_tokens.weight"].float()
+    weights["model.embed_tokens.weight"] = embedding * (1 + 1e-4)   # differs in float32, the same once cast to bfloat16
+    weights["lm_head.weight"] = embedding
+    folder = folder_with(tmp_path, TINY_A, weights)
+    load_weights(build(TINY_A), folder, device="cpu", dtype=torch.bfloat16)
+    with pytest.raises(WeightError, match="tied tensors with different values"):
+        load_weights(build(TINY_A), folder, device="cpu", dtype=torch.float32)
 
 
 def test_tied_weights_either_name_or_both_if_equal(tmp_path):

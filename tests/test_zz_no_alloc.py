@@ -92,3 +92,39 @@ def test_no_alloc_entry_point_refuses_what_its_array_cannot_hold():
     message = lib.qil_last_error().decode()
     assert "floats of scratch" in message and "4194304" in message
     assert torch.isnan(out.float()).all()                    # nothing was launched
+
+
+def test_the_two_entry_points_of_one_library_share_the_kernels_shared_memory_limit():
+    """The regular entry point of the same library with a short span, then the no-allocation one with the longest
+    span: the first must not have lowered the kernel's shared-memory limit under what the second needs."""
+    lib = load_library()
+    lib.qil_attn_decode.restype = c_int
+    short = decode_case([100, 64], n_q=8, n_kv=2, page=16, seed=43, span_len=64)
+    n = short["q"].shape[0]
+    slots = n * short["n_q"] * short["n_spans"]
+    part_o = torch.empty(slots * HEAD_DIM, dtype=torch.float32, device="cuda")
+    part_ml = torch.empty(slots * 2, dtype=torch.float32, device="cuda")
+    out = torch.full_like(short["q"], float("nan"))
+    ptr = lambda t: c_void_p(t.data_ptr())
+    code = lib.qil_attn_decode(
+        ptr(short["q"]), ptr(short["pool"]), ptr(out), ptr(short["decode_info"]), c_int(n), ptr(part_o), ptr(part_ml),
+        c_int(short["n_spans"]), c_int(short["span_len"]), ptr(short["table"]), c_int(short["table"].shape[1]),
+        c_int(short["n_q"]), c_int(short["n_kv"]), c_int(short["page"]), c_int(short["pool"].shape[0]), c_int(0),
+        c_float(HEAD_DIM ** -0.5), c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert code == 0, lib.qil_last_error().decode()
+    torch.testing.assert_close(out.float().cpu(), short["expected"].float(), atol=8e-3 * 2, rtol=8e-3)
+    long = decode_case([2000, 5], n_q=8, n_kv=2, page=4, seed=44, span_len=2048)     # many more page ids per span
+    code, got = no_alloc(lib, long)
+    torch.cuda.synchronize()
+    assert code == 0, lib.qil_last_error().decode()
+    torch.testing.assert_close(got.float().cpu(), long["expected"].float(), atol=8e-3 * 2, rtol=8e-3)
+
+
+def test_spans_that_do_not_reach_a_token_give_nan_not_a_shortened_softmax():
+    lib = load_library()
+    case = decode_case([300, 40], n_q=8, n_kv=2, page=16, seed=45, span_len=64)      # needs 5 spans
+    code, out = no_alloc(lib, case, n_spans=3)                                        # 192 positions: the first token is beyond
+    torch.cuda.synchronize()
+    assert code == 0
+    assert torch.isnan(out[0].float()).all()
+    torch.testing.assert_close(out[1].float().cpu(), case["expected"][1].float(), atol=8e-3 * 2, rtol=8e-3)
