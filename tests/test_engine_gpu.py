@@ -129,7 +129,10 @@ def test_running_a_step_ahead_gives_the_same_tokens(models, monkeypatch):
     prompts = [harness.random_tokens(cfg, n, 200 + n) for n in (5, 17, 33, 9, 2)]
     settings = [dict(max_new_tokens=10), dict(max_new_tokens=7, temperature=0.8, seed=11), dict(max_new_tokens=12),
                 dict(max_new_tokens=1), dict(max_new_tokens=9)]
-    stop_token = plain.greedy(prompts[2], 12, weights, cfg)[4]       # the third request stops on its fifth token
+    greedy = plain.greedy(prompts[2], 12, weights, cfg)
+    # the third request stops in mid-run, on a token that it has not generated before
+    stop_at = max(k for k in range(1, 9) if greedy[k] not in greedy[:k])
+    stop_token = greedy[stop_at]
     def run(overlap):
         engine = Engine(model, num_pages=40, page_size=8, token_budget=16, prefill_chunk=8, max_active=3,
                         overlap=overlap)
@@ -152,7 +155,7 @@ def test_running_a_step_ahead_gives_the_same_tokens(models, monkeypatch):
     ahead_rows, ahead_events, ahead_calls = run(True)
     for a, b in zip(plain_rows, ahead_rows):
         assert a["token_ids"] == b["token_ids"] and a["finish_reason"] == b["finish_reason"] and b["state"] == "completed"
-    assert plain_rows[2]["finish_reason"] == "eos" and len(plain_rows[2]["token_ids"]) == 5
+    assert plain_rows[2]["finish_reason"] == "eos" and plain_rows[2]["token_ids"] == greedy[:stop_at + 1]
     assert plain_rows[3]["token_ids"] == plain.greedy(prompts[3], 1, weights, cfg)
     assert sorted(plain_events) == sorted(ahead_events)
     assert ahead_calls >= plain_calls

@@ -17,23 +17,23 @@ ROOT = Path(__file__).resolve().parent.parent
 BLOCKED = ("triton", "transformers", "vllm", "nano_vllm", "flash_attn", "flashinfer", "cutlass", "tilelang", "xformers")
 
 RUNNER = """
-import importlib.abc, json, sys
+import builtins, json, sys
 
 BLOCKED = {blocked!r}
+original = builtins.__import__
 
-class Refuse(importlib.abc.MetaPathFinder):
-    def find_spec(self, name, path=None, target=None):
-        if name.split(".")[0] in BLOCKED:
-            raise ImportError(f"import of {{name}} is blocked in this test")
-        return None
+def restricted(name, *args, **kwargs):
+    if name.split(".")[0] in BLOCKED:
+        raise ImportError("import of " + name + " is blocked in this test")
+    return original(name, *args, **kwargs)
 
-sys.meta_path.insert(0, Refuse())
+builtins.__import__ = restricted
 for name in BLOCKED:
     try:
         __import__(name)
     except ImportError:
         continue
-    raise SystemExit(f"{{name}} could still be imported")
+    raise SystemExit(name + " could still be imported")
 from qwen_inference_lab_b200.__main__ import main
 code = main({argv!r})
 loaded = sorted(name for name in sys.modules if name.split(".")[0] in BLOCKED)

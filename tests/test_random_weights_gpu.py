@@ -48,7 +48,7 @@ def test_a_model_drawn_on_the_device_is_the_model_of_the_written_folder(tmp_path
     assert torch.equal(rows[0], rows[1])
     # and the folder is an oracle for the drawn model: the plain implementation reads it
     with SafetensorsFile(folder / "model.safetensors") as f:
-        weights = {name: f.tensor(name).float() for name in f.keys()}
+        weights = {name: f.tensor(name).float().clone() for name in f.keys()}      # the views die with the file
     if cfg.get("tie_word_embeddings", True):
         weights.setdefault("lm_head.weight", weights["model.embed_tokens.weight"])
     from tests.plain import qwen3_plain as plain

@@ -269,7 +269,7 @@ def toy(tmp_path_factory):
         config = ToyConfig()
         folder = write_model_folder(config, 11, tmp_path_factory.mktemp("toy"))
         with SafetensorsFile(folder / "model.safetensors") as f:
-            weights = {name: f.tensor(name).float() for name in f.keys()}
+            weights = {name: f.tensor(name).float().clone() for name in f.keys()}
         yield config, folder, weights
     finally:
         registry.unregister(ToyConfig.architecture)
