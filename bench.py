@@ -259,7 +259,7 @@ class OursBench:
         for _ in range(batch):
             prompt = torch.randint(0, self.cfg["vocab_size"], (prompt_len,), generator=generator).tolist()
             engine.submit(prompt, max_new_tokens=new_tokens, ignore_eos=True)
-        while any(r.computed < len(r.prompt) for r in engine.scheduler.requests.values()):
+        while engine.scheduler.prefilling:
             engine.step()
         for _ in range(warmup):
             engine.step()

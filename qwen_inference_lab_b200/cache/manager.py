@@ -7,7 +7,9 @@ free list and one block table per request; a page id addresses the same slot ran
 in every member layer's plane, as in the reference's pool (qil/cache.py:47-49).
 A group with a window gives pages back as soon as the window has passed them; the
 others keep theirs until the request ends.  A state group is an array with one
-slot per request row, zeroed at admission.
+slot per request row, zeroed at admission.  Whoever runs requests may keep state of
+its own in such slots too (``request_state``: the engine keeps each request's sampling
+settings and draw count there), beside the slots that layers own.
 
 Admission can reserve capacity for the whole request (credits only: no page is
 taken until tokens arrive), so that several partial prefills can never exhaust
@@ -83,7 +85,7 @@ class _KVGroup:
 
 class CacheManager:
     def __init__(self, specs, *, num_pages, page_size, max_requests, max_context, dtype, device,
-                 max_step_tokens=None):
+                 max_step_tokens=None, request_state=None):
         if any(type(v) is not int or v < 1 for v in (num_pages, page_size, max_requests, max_context)):
             raise CacheError("cache dimensions must be positive integers")
         self.page_size, self.num_pages = page_size, num_pages
@@ -114,6 +116,9 @@ class CacheManager:
                 self.state_groups.append((spec, members, tensor))
             else:
                 raise CacheError(f"unknown cache spec {spec!r}")
+        # state that belongs to a request, not to a layer: name -> tensor [max_requests, *shape]
+        self._request_state = {name: torch.zeros((max_requests, *spec.shape), dtype=spec.dtype, device=device)
+                               for name, spec in (request_state or {}).items()}
         self._ring = PinnedRing(depth=8) if self.device.type == "cuda" else None
         self.free_rows = deque(range(max_requests))
         self.rows: dict = {}       # request -> row
@@ -167,7 +172,14 @@ class CacheManager:
                 g.reserved[request_id] = g.credit(limit, self.max_step_tokens)
         for _, _, tensor in self.state_groups:
             tensor[:, row].zero_()
+        for tensor in self._request_state.values():
+            tensor[row].zero_()
         return True
+
+    def request_state(self, name) -> torch.Tensor:
+        """The slots of the per-request state ``name`` given at construction: [max_requests, *shape],
+        indexed by ``row(request_id)``, zeroed when a request is admitted."""
+        return self._request_state[name]
 
     def row(self, request_id) -> int:
         return self.rows[request_id]

@@ -6,6 +6,11 @@
 // sum, which draws from softmax(logit / temperature).  The noise of vocabulary
 // entry i is a pure function of (seed, draw counter, i), so a request's tokens do
 // not depend on which other requests share the batch.
+//
+// The settings of a row come either from three arrays the caller uploads (temperature, seed, draw
+// counter per row) or from the requests' state slots: ``state`` int64 [slots, 4] holds, per request,
+// (the temperature's float bits, the seed, the number of draws so far, unused) and ``owner`` names each
+// row's slot.  With slots the kernel counts the draws itself, so a step uploads nothing for sampling.
 #include "common.cuh"
 
 __device__ __forceinline__ float qil_uniform(unsigned long long seed, unsigned long long counter,
@@ -36,17 +41,20 @@ __device__ __forceinline__ void sample_better(float& bv, int& bi, float ov, int 
 __global__ void __launch_bounds__(256)
 sample_rows_kernel(const float* __restrict__ logits, int vocab, long long row_stride, int splits, int slice,
                    const float* __restrict__ temperature, const long long* __restrict__ seed,
-                   const long long* __restrict__ counter, int* __restrict__ token_out,
-                   int* __restrict__ nonfinite_out) {
+                   const long long* __restrict__ counter, long long* __restrict__ state,
+                   const int* __restrict__ owner, int* __restrict__ token_out, int* __restrict__ nonfinite_out) {
     __shared__ float best_v[8];
     __shared__ int best_i[8];
     __shared__ int bad_s[8];
     __shared__ int is_last;
     const int row = blockIdx.y, split = blockIdx.x;
     const float* x = logits + (size_t)row * row_stride;
-    const float temp = temperature ? temperature[row] : 0.f;
-    const unsigned long long sd = seed ? (unsigned long long)seed[row] : 0ull;
-    const unsigned long long ct = counter ? (unsigned long long)counter[row] : 0ull;
+    long long* const slot_state = state ? state + (size_t)owner[row] * 4 : nullptr;
+    // every block of the row reads the draw count before it takes its ticket; the block that takes the last
+    // ticket moves the count on
+    const float temp = slot_state ? __int_as_float((int)slot_state[0]) : (temperature ? temperature[row] : 0.f);
+    const unsigned long long sd = slot_state ? (unsigned long long)slot_state[1] : (seed ? (unsigned long long)seed[row] : 0ull);
+    const unsigned long long ct = slot_state ? (unsigned long long)slot_state[2] : (counter ? (unsigned long long)counter[row] : 0ull);
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     int bad = 0;
@@ -78,7 +86,10 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, long long row_st
         __threadfence();
         const unsigned drawn = atomicAdd(&sample_tickets[row], 1u);
         is_last = drawn == (unsigned)splits - 1u;
-        if (is_last) sample_tickets[row] = 0u;
+        if (is_last) {
+            sample_tickets[row] = 0u;
+            if (slot_state) slot_state[2] = (long long)(ct + 1ull);
+        }
     }
     __syncthreads();
     if (!is_last || threadIdx.x >= 32) return;
@@ -103,9 +114,13 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, long long row_st
 
 extern "C" int qil_sample_rows(const float* logits, int n_rows, int vocab, long long row_stride,
                                const float* temperature, const long long* seed, const long long* counter,
-                               int* token_out, int* nonfinite_out, cudaStream_t stream) {
+                               long long* state, const int* owner, int* token_out, int* nonfinite_out,
+                               cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0 || row_stride < vocab) QIL_REFUSE("sample_rows: vocab %d row stride %lld", vocab, row_stride);
+    if ((state == nullptr) != (owner == nullptr)) QIL_REFUSE("sample_rows: state slots need the rows' owners, and the reverse");
+    if (state != nullptr && (temperature || seed || counter))
+        QIL_REFUSE("sample_rows: settings come from state slots or from arrays, not both");
     int splits = (vocab + 2047) / 2048;
     if (splits > SAMPLE_SPLITS) splits = SAMPLE_SPLITS;
     const int slice = (vocab + splits - 1) / splits;
@@ -114,7 +129,8 @@ extern "C" int qil_sample_rows(const float* logits, int n_rows, int vocab, long 
         sample_rows_kernel<<<dim3(splits, rows), 256, 0, stream>>>(
             logits + (size_t)first * row_stride, vocab, row_stride, splits, slice,
             temperature ? temperature + first : nullptr, seed ? seed + first : nullptr,
-            counter ? counter + first : nullptr, token_out + first, nonfinite_out + first);
+            counter ? counter + first : nullptr, state, owner ? owner + first : nullptr, token_out + first,
+            nonfinite_out + first);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }
     }

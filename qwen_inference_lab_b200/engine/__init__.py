@@ -1,3 +1,3 @@
 from .step import StepEntry, StepError, StepRunner
-from .scheduler import Request, Scheduler, Work
+from .scheduler import Scheduler, Sequence, Turn
 from .engine import Engine

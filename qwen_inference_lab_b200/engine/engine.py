@@ -22,9 +22,18 @@ from __future__ import annotations
 from time import perf_counter
 
 from ..cache import CacheManager
-from ..sampling import Sampler
-from .scheduler import Request, Scheduler
-from .step import PENDING, StepEntry, StepRunner
+from ..sampling import SLOT, Sampler
+from .scheduler import ACTIVE, Scheduler, Sequence
+from .step import StepRunner
+
+
+class _Flight:
+    """A step that has been queued on the GPU: its turns, the sequences it chooses tokens for (in the order
+    of the sampler's rows) and the sampler's ticket for them."""
+    __slots__ = ("turns", "sampling", "ticket")
+
+    def __init__(self, turns, sampling, ticket):
+        self.turns, self.sampling, self.ticket = turns, sampling, ticket
 
 
 class Engine:
@@ -32,13 +41,14 @@ class Engine:
                  max_active=4, clock=perf_counter, seed=0, use_graphs=True, overlap=False):
         self.model = model
         self.overlap = bool(overlap)
-        self._queued = None           # the step that is on the GPU and whose tokens the host has not read
         self.clock = clock
         self.seed = int(seed)
         self.next_id = 0
+        self._in_flight = None        # the step that is on the GPU and whose tokens the host has not read
         self.cache = CacheManager(model.cache_specs(), num_pages=num_pages, page_size=page_size,
                                   max_requests=max_active, max_context=model.max_positions,
-                                  dtype=model.dtype, device=model.device, max_step_tokens=token_budget)
+                                  dtype=model.dtype, device=model.device, max_step_tokens=token_budget,
+                                  request_state={"sampler": SLOT})
         self.scheduler = Scheduler(self.cache, token_budget=token_budget, prefill_chunk=prefill_chunk,
                                    max_active=max_active)
         self.runner = StepRunner(model, self.cache, max_step_tokens=token_budget, use_graphs=use_graphs)
@@ -50,167 +60,143 @@ class Engine:
     def pool(self):
         return self.cache
 
-    def submit(self, prompt, *, max_new_tokens=64, ignore_eos=False, temperature=0.0, seed=None):
-        prompt = list(prompt)
+    # ------------------------------------------------------------------ requests in
+    def _check_submission(self, prompt, max_new_tokens, temperature, seed) -> None:
+        """The reference's three checks (qil/engine.py:35-40), then the sampling settings."""
         vocab = self.model.vocab_size
-        if not prompt or any(type(t) is not int or not 0 <= t < vocab for t in prompt):
-            raise ValueError("prompt must contain valid integer token IDs")
-        if type(max_new_tokens) is not int or max_new_tokens < 1:
-            raise ValueError("max_new_tokens must be a positive integer")
-        if len(prompt) + max_new_tokens > self.model.max_positions:
-            raise ValueError("request exceeds model context length")
-        if isinstance(temperature, bool) or not isinstance(temperature, (int, float)) or not temperature >= 0 \
-                or temperature == float("inf"):
+        if len(prompt) == 0:
+            raise ValueError("the prompt is empty; it must hold at least one token id")
+        for token in prompt:
+            if type(token) is not int or token < 0 or token >= vocab:
+                raise ValueError(f"the prompt holds {token!r}; token ids must be integers in [0, {vocab})")
+        if type(max_new_tokens) is not int or max_new_tokens <= 0:
+            raise ValueError(f"max_new_tokens must be a positive integer, got {max_new_tokens!r}")
+        room = self.model.max_positions
+        if len(prompt) + max_new_tokens > room:
+            raise ValueError(f"{len(prompt)} prompt tokens and {max_new_tokens} new ones exceed the model's "
+                             f"context length of {room} positions")
+        number = isinstance(temperature, (int, float)) and not isinstance(temperature, bool)
+        if not number or not 0 <= temperature < float("inf"):
             raise ValueError("temperature must be a finite number >= 0")
         if seed is not None and type(seed) is not int:
             raise ValueError("seed must be an integer")
-        eos = set() if ignore_eos else set(getattr(self.model.config, "eos_token_ids", ()))
+
+    def submit(self, prompt, *, max_new_tokens=64, ignore_eos=False, temperature=0.0, seed=None):
+        prompt = list(prompt)
+        self._check_submission(prompt, max_new_tokens, temperature, seed)
+        stops = () if ignore_eos else getattr(self.model.config, "eos_token_ids", ())
         request_id = self.next_id
-        request_seed = seed if seed is not None else self.seed * 1000003 + request_id
-        self.scheduler.add(Request(request_id, prompt, max_new_tokens, eos, self.clock(),
-                                   temperature=float(temperature), seed=request_seed))
-        self.next_id += 1
+        if seed is None:
+            seed = self.seed * 1000003 + request_id
+        self.scheduler.add(Sequence(request_id, prompt, max_new_tokens, stops, self.clock(),
+                                    temperature=temperature, seed=seed))
+        self.next_id = request_id + 1
         return request_id
 
+    # ------------------------------------------------------------------ steps
     def step(self) -> list:
         """Run one planned batch; returns events ``dict(request_id, token_id, timestamp_s, finished)``:
         of this batch, or with ``overlap`` of the batch queued by the call before."""
+        earlier = self._in_flight if self.overlap else None
+        turns = self.scheduler.plan()
+        try:
+            flight = self._launch(turns, earlier)
+        except Exception as error:
+            self._in_flight = None
+            if earlier is not None:
+                self._land(earlier, quiet=True)        # its tokens are kept; the error below is the news
+            self._fail(turns, error)
+            raise
         if self.overlap:
-            return self._step_ahead()
-        plan = self.scheduler.plan()
-        try:
-            queued = self._queue(plan, None)
-        except Exception as error:
-            self._fail(plan, error)
-            raise
-        return self._collect(queued) if queued is not None else []
+            self._in_flight = flight
+            return self._land(earlier) if earlier is not None else []
+        return self._land(flight) if flight is not None else []
 
-    def _step_ahead(self) -> list:
-        before = self._queued
-        plan = self.scheduler.plan()
-        try:
-            self._queued = self._queue(plan, before)
-        except Exception as error:
-            self._queued = None
-            if before is not None:
-                self._collect(before, quiet=True)       # its tokens are kept; the error below is the news
-            self._fail(plan, error)
-            raise
-        return self._collect(before) if before is not None else []
-
-    def _queue(self, plan, before):
-        """Queue a plan's step and the choice of its tokens; nothing waits.  ``before``: the step whose
-        tokens are still on the device (requests with a pending token take it from there)."""
-        if not plan:
+    def _launch(self, turns, earlier):
+        """Queue a plan's step and the choice of its tokens; nothing waits.  ``earlier``: the step whose
+        tokens are still on the device (entries with a pending token take it from there)."""
+        if not turns:
             return None
-        requests = self.scheduler.requests
-        entries, ready = [], []
-        for work in plan:
-            request = requests[work.request_id]
-            done = work.start + len(work.tokens) == request.input_length
-            feed = None
-            if work.tokens[-1] == PENDING:
-                feed = before["slot"][request.id]
-            entries.append(StepEntry(work.request_id, work.tokens, [len(work.tokens) - 1] if done else [], feed))
-            if done:
-                ready.append(request)
-        source = before["ticket"].tokens if before is not None and before["ticket"] is not None else None
-        logits = self.runner.run(entries, source)
+        source = earlier.ticket.tokens if earlier is not None and earlier.ticket is not None else None
+        logits = self.runner.run([turn.entry for turn in turns], source)
+        sampling = [turn.sequence for turn in turns if turn.samples]
         ticket = None
-        if ready:
-            ticket = self.sampler.begin(logits, [r.temperature for r in ready], [r.seed for r in ready],
-                                        [len(r.output) + r.pending for r in ready])
-        for work in plan:
-            requests[work.request_id].computed = work.start + len(work.tokens)
-        for request in ready:
-            request.pending += 1          # 2 for a moment when running ahead: this step's and the one before's
-        return dict(plan=plan, ready=ready, ticket=ticket, slot={r.id: i for i, r in enumerate(ready)})
+        if sampling:
+            state = self.cache.request_state("sampler")
+            for sequence in sampling:
+                if sequence.temperature > 0 and not sequence.sampler_ready:
+                    self.sampler.configure(state, self.cache.row(sequence.id), sequence.temperature, sequence.seed)
+                    sequence.sampler_ready = True
+            ticket = self.sampler.begin(logits, state=state, owner=self.runner.logit_owner)
+        self.scheduler.queued(turns)
+        return _Flight(turns, sampling, ticket)
 
-    def _fail(self, plan, error):
-        for work in plan:
-            request = self.scheduler.requests[work.request_id]
-            if request.state == "active":
-                request.error = str(error)
-                request.pending = 0
-                self.scheduler.retire(work.request_id, "failed", "error")
+    def _fail(self, turns, error) -> None:
+        """A step that failed may have left any of its requests with partly written pages: all of them end
+        as failed and free their cache; requests outside the batch go on (qil/engine.py:87-93)."""
+        for turn in turns:
+            if turn.sequence.state == ACTIVE:
+                turn.sequence.error = str(error)
+                self.scheduler.retire(turn.sequence.id, "failed", "error")
 
-    def _collect(self, queued, quiet=False) -> list:
+    def _land(self, flight, quiet=False) -> list:
         """Wait for a queued step's tokens; append them, retire what finished, return the events."""
-        plan, ready = queued["plan"], queued["ready"]
-        requests = self.scheduler.requests
         try:
-            tokens = self.sampler.finish(queued["ticket"]) if queued["ticket"] is not None else []
+            tokens = self.sampler.finish(flight.ticket) if flight.ticket is not None else []
             self.runner.check(wait=not self.overlap)     # kernels with bounded waits report through error words
         except Exception as error:
-            self._fail(plan, error)
+            self._fail(flight.turns, error)
             if quiet:
                 return []
             raise
-        self.counters["steps"] += 1
-        for work in plan:
-            count = len(work.tokens)
-            self.counters["tokens"] += count
-            prompt_length = len(requests[work.request_id].prompt)
-            self.counters["prefill_tokens" if work.start < prompt_length else "decode_tokens"] += count
+        counters = self.counters
+        counters["steps"] += 1
+        for turn in flight.turns:
+            counters["tokens"] += turn.count
+            counters["prefill_tokens" if turn.start < len(turn.sequence.prompt) else "decode_tokens"] += turn.count
         events = []
-        for request, token in zip(ready, tokens):
-            if request.state != "active" or not request.pending:
-                continue                # cancelled, failed or finished since: the token is dropped
-            observed = self.clock()
-            request.pending -= 1
-            request.output.append(token)
-            request.token_times_s.append(observed)
-            reason = "eos" if token in request.eos else (
-                "length" if len(request.output) == request.max_new_tokens else None)
-            if reason:
-                self.scheduler.retire(request.id, "completed", reason)
-            events.append(dict(request_id=request.id, token_id=token, timestamp_s=observed,
-                               finished=reason is not None))
+        for sequence, token in zip(flight.sampling, tokens):
+            event = self.scheduler.read(sequence, token, self.clock())
+            if event is not None:
+                events.append(event)
         return events
 
+    # ------------------------------------------------------------------ requests out
     def cancel(self, request_id) -> bool:
         return self.scheduler.retire(request_id, "cancelled", "cancelled")
 
     def result(self, request_id) -> dict:
-        request = self.scheduler.requests[request_id]
-        times = request.token_times_s
-        gaps = [b - a for a, b in zip(times, times[1:])]
-        return dict(
-            request_id=request_id, state=request.state, finish_reason=request.finish_reason,
-            error=request.error, token_ids=list(request.output),
-            token_times_s=[t - request.arrival_s for t in times],
-            ttft_s=times[0] - request.arrival_s if times else None,
-            e2e_s=times[-1] - request.arrival_s if request.state == "completed" else None,
-            tpot_s=sum(gaps) / len(gaps) if gaps else None)
+        return self.scheduler.table[request_id].report()
 
     @property
     def idle(self) -> bool:
-        return self.scheduler.idle and self._queued is None
+        return self._in_flight is None and self.scheduler.idle
 
     def generate(self, prompts, *, max_new_tokens=64, ignore_eos=False, temperature=0.0, seed=None) -> list:
+        """Submit all prompts, step until nothing is left, return their results in order.  Runs a step ahead
+        of the host (nobody reads the events here).  On an error every request of the call is cancelled."""
         if not self.idle:
-            raise ValueError("generate requires an idle engine; use submit/step for live requests")
-        request_ids = []
+            raise ValueError("generate() needs an idle engine; feed a busy one with submit() and step()")
+        mine = []
+        mode, self.overlap = self.overlap, True
         try:
             for index, prompt in enumerate(prompts):
-                request_ids.append(self.submit(
-                    prompt, max_new_tokens=max_new_tokens, ignore_eos=ignore_eos, temperature=temperature,
-                    seed=None if seed is None else seed + index))
-            ahead, self.overlap = self.overlap, True       # nobody reads the events here: run a step ahead
-            try:
-                while not self.idle:
-                    self.step()
-            finally:
-                self.overlap = ahead
+                mine.append(self.submit(prompt, max_new_tokens=max_new_tokens, ignore_eos=ignore_eos,
+                                        temperature=temperature, seed=seed if seed is None else seed + index))
+            while not self.idle:
+                self.step()
         except Exception:
-            for request_id in request_ids:
+            for request_id in mine:
                 self.cancel(request_id)
             raise
-        return [self.result(request_id) for request_id in request_ids]
+        finally:
+            self.overlap = mode
+        return [self.result(request_id) for request_id in mine]
 
     def close(self) -> None:
-        for request_id in list(self.scheduler.active) + list(self.scheduler.waiting):
-            self.cancel(request_id)
-        if self._queued is not None:
-            queued, self._queued = self._queued, None
-            self._collect(queued, quiet=True)
+        """Cancel whatever has not ended and wait for the step that may still be on the GPU."""
+        for sequence in [*self.scheduler.ring, *self.scheduler.queue]:
+            self.cancel(sequence.id)
+        flight, self._in_flight = self._in_flight, None
+        if flight is not None:
+            self._land(flight, quiet=True)

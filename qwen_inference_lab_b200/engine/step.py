@@ -75,6 +75,9 @@ class StepRunner:
         self.kernel_launches = 0          # this engine's own kernels (library products are not counted)
         self.launches_per_graph: dict = {}
         self.last_upload_bytes = 0
+        # the request row behind each row of the logits that the last ``run`` returned (int32, on the device;
+        # valid until the next ``run`` uploads its description)
+        self.logit_owner = None
 
     def _reserve(self, ints):
         if ints <= self._capacity:
@@ -166,12 +169,13 @@ class StepRunner:
         positions = np.arange(n) - first[seg_of_token] + starts[seg_of_token]
         token_row = rows[seg_of_token]
         logit_rows = np.array([first[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int64)
+        logit_owner = np.array([rows[i] for i, e in enumerate(entries) for _ in e.want], dtype=np.int64)
         # places of tokens that are still on the device: (index in the flat batch, index in the source buffer)
         feed = np.array([v for i, e in enumerate(entries) if e.feed is not None
                          for v in (first[i] + lens[i] - 1, e.feed)], dtype=np.int64)
         sections = [("token_ids", token_ids), ("positions", positions), ("token_row", token_row),
                     ("seg_row", rows), ("seg_start", first), ("seg_len", lens), ("seg_pos0", starts),
-                    ("logit_rows", logit_rows)]
+                    ("logit_rows", logit_rows), ("logit_owner", logit_owner)]
         for planner in self.planners:
             for name, values in planner.plan(segments).items():
                 sections.append((f"{planner.key}.{name}", np.asarray(values).reshape(-1)))
@@ -239,6 +243,8 @@ class StepRunner:
         offsets, n = description.offsets, description.segments.n_tokens
         self.cache.flush_tables()
         self._upload(description.packed)
+        begin, count = offsets["logit_owner"]
+        self.logit_owner = self._meta_dev[begin:begin + count]
         feed_begin, feed_count = offsets["feed"]
         if feed_count:
             if token_source is None:

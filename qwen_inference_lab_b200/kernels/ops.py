@@ -376,25 +376,34 @@ def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_h
     return out
 
 
-def sample_rows(logits, temperature=None, seed=None, counter=None, tokens=None, nonfinite=None):
+def sample_rows(logits, temperature=None, seed=None, counter=None, tokens=None, nonfinite=None, state=None,
+                owner=None):
     """Choose one token per row of float32 ``logits`` [R,V]; returns (tokens, nonfinite) int32 [R].
 
-    temperature float32 [R] (0 = greedy), seed and counter int64 [R]; all optional (greedy).
+    Settings per row come from arrays: temperature float32 [R] (0 = greedy), seed and counter int64 [R], all
+    optional (greedy); or from state slots: ``state`` int64 [slots, 4] = (the temperature's float32 bits,
+    seed, draws so far, unused) per request and ``owner`` int32 [R], the slot of each row.  With slots
+    the kernel adds one to the draws of every row's slot.
     """
     _need(logits, "logits", torch.float32, 2)
     rows, vocab = logits.shape
     for name, t, dt in (("temperature", temperature, torch.float32), ("seed", seed, torch.int64),
-                        ("counter", counter, torch.int64)):
+                        ("counter", counter, torch.int64), ("owner", owner, torch.int32)):
         if t is not None:
             _need(t, name, dt, 1)
             if t.shape[0] != rows:
                 raise KernelError(f"sample_rows: {name} needs one entry per row")
+    if state is not None:
+        _need(state, "state", torch.int64, 2)
+        if state.shape[1] != 4 or owner is None:
+            raise KernelError("sample_rows: state slots are int64 [slots, 4] and need the rows' owners")
     if tokens is None:
         tokens = torch.empty(rows, dtype=torch.int32, device=logits.device)
     if nonfinite is None:
         nonfinite = torch.empty(rows, dtype=torch.int32, device=logits.device)
     lib = core()
     _check(lib, lib.qil_sample_rows(_p(logits), c_int(rows), c_int(vocab), c_longlong(logits.stride(0)),
-                                    _p(temperature), _p(seed), _p(counter), _p(tokens), _p(nonfinite), _stream()),
+                                    _p(temperature), _p(seed), _p(counter), _p(state), _p(owner), _p(tokens),
+                                    _p(nonfinite), _stream()),
            "sample_rows")
     return tokens, nonfinite

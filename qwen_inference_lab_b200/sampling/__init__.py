@@ -1,1 +1,1 @@
-from .sampler import NonFiniteLogits, Sampler
+from .sampler import SLOT, NonFiniteLogits, Sampler

@@ -6,12 +6,23 @@ error, not a token (qil/engine.py:96-100).  Temperature: a draw from
 only on (the request's seed, the index of the token being drawn, the vocabulary
 index), so that a request's tokens do not change with the batch it shares.
 The reference samples greedily only.
+
+Two ways to give a row its settings.  ``begin``/``choose`` with host sequences copy three small
+arrays to the device per call.  The engine does not: each request's temperature, seed and number of
+draws live in its state slot on the device (``SLOT``, zeroed at admission = greedy; ``configure``
+writes the first two once, when a request that samples with a temperature is first seen), the
+kernel finds a row's slot through ``owner`` (part of the step's one upload) and counts the draws
+itself, so sampling uploads nothing per step.
 """
 from __future__ import annotations
 
 import torch
 
 from ..kernels import ops
+from ..parts.base import StateSpec
+
+#: per-request sampler state: (the temperature's float32 bits, seed, draws so far, unused)
+SLOT = StateSpec((4,), torch.int64)
 
 
 class NonFiniteLogits(RuntimeError):
@@ -51,8 +62,18 @@ class Sampler:
             self._views[rows] = views
         return views
 
-    def begin(self, logits, temperatures=None, seeds=None, counters=None):
+    def configure(self, state, row, temperature, seed) -> None:
+        """Write a request's settings into its slot (``state`` int64 [slots, 4]); its draw count starts at 0.
+        Only requests that sample with a temperature need this: a zeroed slot is greedy."""
+        bits = torch.tensor([temperature], dtype=torch.float32).view(torch.int32).item()
+        values = torch.tensor([bits, seed & 0x7FFFFFFFFFFFFFFF, 0, 0], dtype=torch.int64)
+        if self.device.type == "cuda":
+            values = values.pin_memory()
+        state[row].copy_(values, non_blocking=True)
+
+    def begin(self, logits, temperatures=None, seeds=None, counters=None, *, state=None, owner=None):
         """Queue the choice for every row of ``logits`` and its copy to the host; nothing waits.
+        Settings from host sequences, or from the requests' slots (``state``, ``owner``: see the module's text).
 
         Returns a ticket for ``finish``; ``ticket.tokens`` is the int32 device tensor [R] that holds the
         chosen ids once the stream gets there (the next step may read it on the stream before the
@@ -73,7 +94,7 @@ class Sampler:
             s = torch.tensor([v & 0x7FFFFFFFFFFFFFFF for v in seeds], dtype=torch.int64).to(self.device, non_blocking=True)
             c = torch.tensor(list(counters), dtype=torch.int64).to(self.device, non_blocking=True)
         tokens = device[0, :rows]
-        ops.sample_rows(logits, t, s, c, tokens=tokens, nonfinite=device[1, :rows])
+        ops.sample_rows(logits, t, s, c, tokens=tokens, nonfinite=device[1, :rows], state=state, owner=owner)
         host[:, :rows].copy_(device[:, :rows], non_blocking=True)
         event.record()
         return _Ticket(tokens, host_numpy, event, rows)

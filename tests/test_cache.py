@@ -134,6 +134,20 @@ def test_state_slots_are_zeroed_at_admission_and_follow_the_row():
     assert cache.row("c") == 0 and views[0].slots[0].eq(0).all() and views[2].slots[0].eq(0).all()
 
 
+def test_state_that_belongs_to_requests_not_layers():
+    cache = CacheManager([KVCacheSpec(1, 4)], num_pages=8, page_size=4, max_requests=3, max_context=64,
+                         dtype=torch.float32, device="cpu", request_state={"sampler": StateSpec((4,), torch.int64)})
+    slots = cache.request_state("sampler")
+    assert slots.shape == (3, 4) and slots.dtype == torch.int64
+    cache.admit("a"); cache.admit("b")
+    slots[cache.row("b")] = torch.tensor([1, 2, 3, 4])
+    cache.release("b")
+    cache.admit("c"); cache.admit("d")            # "d" gets the row "b" had: zeroed again
+    assert cache.row("d") == 1 and slots[1].tolist() == [0, 0, 0, 0]
+    with pytest.raises(KeyError):
+        cache.request_state("nothing")
+
+
 def test_views_follow_the_order_of_a_model_that_shares_caches():
     from qwen_inference_lab_b200.parts import LayerCall
     cache = manager(specs=(FULL, None, FULL))

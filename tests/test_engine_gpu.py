@@ -79,7 +79,7 @@ def test_eos_cancel_arrival_and_failure(models, monkeypatch):
     # the third generated token becomes an end-of-sequence token: it is emitted, then the request stops
     engine = Engine(model, num_pages=16, page_size=4)
     first = engine.submit(prompt, max_new_tokens=6)
-    engine.scheduler.requests[first].eos = {greedy[2]}
+    engine.scheduler.table[first].eos = {greedy[2]}
     second = None
     steps = 0
     while not engine.idle:
@@ -113,8 +113,10 @@ def test_eos_cancel_arrival_and_failure(models, monkeypatch):
     # non-finite logits are an error, not a token
     engine = Engine(model, num_pages=16, page_size=4)
     c = engine.submit(prompt, max_new_tokens=2)
-    monkeypatch.setattr(engine.runner, "run",
-                        lambda *args: torch.full((1, cfg["vocab_size"]), float("nan"), device="cuda"))
+    def broken(*args):
+        engine.runner.logit_owner = torch.zeros(1, dtype=torch.int32, device="cuda")
+        return torch.full((1, cfg["vocab_size"]), float("nan"), device="cuda")
+    monkeypatch.setattr(engine.runner, "run", broken)
     with pytest.raises(RuntimeError, match="non-finite"):
         engine.step()
     assert engine.result(c)["state"] == "failed"
@@ -139,7 +141,7 @@ def test_running_a_step_ahead_gives_the_same_tokens(models, monkeypatch):
         ids, events, calls = [], [], 0
         for prompt, kw in zip(prompts[:4], settings[:4]):
             ids.append(engine.submit(prompt, ignore_eos=True, **kw))
-        engine.scheduler.requests[ids[2]].eos = {stop_token}
+        engine.scheduler.table[ids[2]].eos = {stop_token}
         while not engine.idle:
             got = engine.step()
             calls += 1

@@ -418,6 +418,28 @@ def test_sample_rows_temperature_matches_plain_and_is_batch_independent():
     assert (freq - want).abs().max() < 0.03
 
 
+def test_sample_rows_with_settings_in_state_slots():
+    """Temperature, seed and the number of draws kept per request on the device: the same tokens as with the
+    three uploaded arrays, and the kernel counts the draws itself."""
+    from qwen_inference_lab_b200.sampling import Sampler
+    torch.manual_seed(18)
+    vocab = 70001                           # several slices a row: every block must read the count before it moves
+    logits = torch.randn(3, vocab) * 2
+    state = torch.zeros(6, 4, dtype=torch.int64).cuda()
+    sampler = Sampler("cuda", max_rows=4)
+    sampler.configure(state, 4, 0.8, 11)
+    sampler.configure(state, 1, 1.3, 2**63 + 5)            # seeds are taken modulo 2^63
+    owner = torch.tensor([4, 2, 1], dtype=torch.int32).cuda()      # slot 2 was never configured: greedy
+    for draw in range(3):
+        tokens = sampler.finish(sampler.begin(logits.cuda() + draw, state=state, owner=owner))
+        assert tokens[0] == plain.sample(logits[0] + draw, 0.8, 11, draw)
+        assert tokens[1] == int((logits[1] + draw).argmax())
+        assert tokens[2] == plain.sample(logits[2] + draw, 1.3, 5, draw)
+    assert state[:, 2].cpu().tolist() == [0, 3, 3, 0, 3, 0]
+    with pytest.raises(Exception, match="owners"):
+        ops().sample_rows(logits.cuda(), state=state)
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 16, 8), (3, 200, 96), (8, 129, 136), (9, 64, 4096), (16, 1000, 520)])
 def test_gemm_small_m(m, n, k):
     torch.manual_seed(9)
