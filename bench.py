@@ -10,8 +10,12 @@ intermediate 12288, vocabulary 151936, untied head) with random bfloat16 weights
 steps; ``e2e`` is the same through ``Engine.step`` with host token ids in and
 sampled ids out; ``prefill`` times one 2048-token prompt; ``roofline`` relates the
 bytes a decode step must read (every weight once, the cache of the live requests)
-to the measured copy bandwidth; ``points`` holds decode at batch 1 and 64.
+to the measured copy bandwidth; ``points`` holds decode at batch 1 and 64 at the same
+context and at batch 16, 32 and 64 at a context of 1024 (tokens per second), and
+``points_detail`` their milliseconds, bytes and fraction of the copy bandwidth.
 Peaks come from MEASURED_PEAKS.json beside this file when present.
+``--shape 32b|0.6b`` prints the same line for the other layer sizes; ``--impl reference``
+the same line for the unmodified reference engine.
 """
 from __future__ import annotations
 
@@ -132,6 +136,17 @@ def prefill_flops(cfg, tokens, logit_rows=1):
     gemm = 2.0 * tokens * layer_params + 2.0 * logit_rows * head_params
     attention = cfg["num_hidden_layers"] * 4.0 * cfg["num_attention_heads"] * cfg["head_dim"] * tokens * (tokens + 1) / 2
     return gemm + attention
+
+
+def config_record(cfg, label, batch, context, full_layers, of):
+    """The ``config`` of a bench line: every size by name, flat; the same keys for both arms."""
+    return {"model": label, "layers": cfg["num_hidden_layers"], "layers_of_config": full_layers,
+            "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "tied": cfg["tie_word_embeddings"],
+            "global_batch": batch, "seq_len": context, "page_size": PAGE_SIZE, "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (decode reads >16 GB per step); prefill flushes a 256 MB buffer",
+            "peaks": of}
 
 
 # --------------------------------------------------------------------------- our engine
@@ -324,13 +339,18 @@ def run_ours(args):
               f"({args.prefill_tokens / ms * 1e3:.0f} tokens/s, {frac:.3f} of the bf16 peak; all: {bench.last_prefill_times})")
         return
     main = bench.decode(batch, context, args.steps, args.warmup, sample_clocks=True)
-    points = {}
-    for b in (1, 64):
+    points, points_detail = {}, {}
+    short = min(1024, context)
+    for b, wanted in ((1, context), (64, context), (16, short), (32, short), (64, short)):
         if args.quick:
             break
-        fits = bench.largest_context(b, context)      # the 32B shape holds 64 requests only at a shorter context
+        fits = bench.largest_context(b, wanted)      # the 32B shape holds 64 requests only at a shorter context
         key = f"decode_b{b}" if fits == context else f"decode_b{b}_context{fits}"
-        points[key] = round(bench.decode(b, fits, max(8, args.steps // 2), args.warmup)["tokens_per_s"], 1)
+        part = bench.decode(b, fits, max(8, args.steps // 2), args.warmup)
+        points[key] = round(part["tokens_per_s"], 1)
+        gbs = part["bytes"] / (part["ms_per_step"] * 1e-3) / 1e9
+        points_detail[key] = {"ms": round(part["ms_per_step"], 4), "gbytes": round(part["bytes"] / 1e9, 3),
+                              "gbs": round(gbs, 1), "frac": round(gbs / pk["hbm_gbs"], 4)}
     prefill_ms = bench.prefill(PREFILL_TOKENS)
     e2e = bench.e2e(batch, context, args.steps, args.warmup)
     flops = prefill_flops(cfg, PREFILL_TOKENS)
@@ -342,13 +362,7 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic: random weights, random token ids, random cache contents",
         "impl": "ours",
-        "config": {"model": label, "layers": cfg["num_hidden_layers"], "layers_of_config": bench.full_layers,
-                   "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
-                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "tied": cfg["tie_word_embeddings"],
-                   "global_batch": batch, "seq_len": context, "page_size": PAGE_SIZE, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (decode reads >16 GB per step); prefill flushes a 256 MB buffer",
-                   "peaks": of},
+        "config": config_record(cfg, label, batch, context, bench.full_layers, of),
         "clocks": main["clocks"],
         "e2e": {k: (round(v, 2) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": int(main["launches"]),
@@ -360,7 +374,7 @@ def run_ours(args):
                     "sm_mhz": bench.last_prefill_clocks["sm_mhz"], "reasons": bench.last_prefill_clocks["reasons"]},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points,
+        "points": points, "points_detail": points_detail,
     }
     print(json.dumps(line), flush=True)
 
@@ -421,15 +435,22 @@ def run_reference(args):
         return unavailable(f"the reference failed on this configuration: {type(error).__name__}: {str(error)[:200]}")
     pk = peaks()
     achieved = decode_bytes(QWEN3_8B, batch, CONTEXT) / (ms * 1e-3) / 1e9
+    of = "of measured" if pk["source"] == "measured" else "of fallback"
+    # What the reference copies per decode step (qil/model.py:143-152, qil/cache.py:103-131, qil/engine.py:96-100):
+    # it builds int64 tensors from Python lists for the token ids, the positions (lengths derive from them on the
+    # device), the write slots and the padded page table, and reads back one flag and the chosen ids.
+    table_width = (CONTEXT + args.warmup + args.steps + PAGE_SIZE - 1) // PAGE_SIZE
+    h2d = 8 * (batch + batch + batch + batch * table_width)
+    d2h = 1 + 8 * batch
     print(json.dumps({
         "metric": "decode tokens/s (Qwen3-8B shape, batch 8, context 8192)", "impl": "reference",
         "value": round(batch / ms * 1e3, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights, random token ids",
-        "config": {"model": "Qwen3-8B shape", "global_batch": batch, "seq_len": CONTEXT, "page_size": PAGE_SIZE,
-                   "decode_attention": "paged", "parallelism": "single GPU"},
+        "config": config_record(QWEN3_8B, "Qwen3-8B shape", batch, CONTEXT, QWEN3_8B["num_hidden_layers"], of),
         "clocks": sampler.summary(),
-        "e2e": {"value": round(emitted / elapsed, 2), "unit": "tokens/s", "note": "Engine.step with host ids in and out"},
+        "e2e": {"value": round(emitted / elapsed, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(elapsed / args.steps * 1e3, 2)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
     }), flush=True)

@@ -26,6 +26,8 @@
  *    A call needs  n_decode * n_q_heads * n_spans * (head_dim + 2)  floats, rounded up
  *    to a multiple of 64; a call that needs more returns -1 and qil_last_error()
  *    says by how much.  Nothing is launched in that case.
+ *    A call also uses one counter per (token, kv head, 16 query heads of that kv head) from
+ *    a second fixed array of 65536 counters; more than that is refused the same way.
  *  - It calls no cudaMalloc, cudaFree or any routine that allocates.
  *  - The first call on each device looks up the array's device address and sets
  *    a kernel attribute; make that first call outside any stream capture, with
@@ -37,7 +39,8 @@
  *    at a time per device, or put your own lock around them.
  *  - All calls share the one array, and it keeps what the last call left in it.
  *    Nothing in it has to start at zero: every slot a call reads, that call wrote
- *    first.  Two calls whose kernels overlap on the GPU (different streams, no
+ *    first.  The counters must start at zero: each call clears the ones it uses on the
+ *    stream before its kernel runs.  Two calls whose kernels overlap on the GPU (different streams, no
  *    ordering between them) race on the array; order them.
  *
  * Returns 0 when the kernels were queued on `stream`, a positive cudaError_t if a

@@ -400,7 +400,8 @@ __device__ __forceinline__ void warp_norm_rotate_head(const bf16* __restrict__ s
 // part_o  [n_decode, Hq, n_spans, D] float32, unnormalised; part_ml [n_decode, Hq, n_spans, 2] (max, sum).
 __global__ void __launch_bounds__(128)
 attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int n_spans, int span_len_arg, DecodeTail tail) {
+                        float* __restrict__ part_ml, unsigned* __restrict__ tickets, int n_spans, int span_len_arg,
+                        DecodeTail tail) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [16][LDS]
     bf16* sK = sQ + 16 * LDS;                           // [2][64][LDS]
@@ -420,7 +421,7 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
     const int span_len = span_len_arg > 0 ? span_len_arg : span_len_of(info.w, n_spans, -span_len_arg);
     const int k_begin = span * span_len;
-    if (k_begin > hi || k_begin + span_len <= lo) return;    // the merge skips the same spans
+    if (k_begin > hi || k_begin + span_len <= lo) return;    // takes no ticket: the merge counts the same spans
     const int* table = p.block_table + (size_t)info.z * p.table_stride;
     const int first_tile = max(k_begin, lo) / KV_TILE;
     const int last_tile = min(k_begin + span_len - 1, hi) / KV_TILE;
@@ -617,6 +618,14 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
         wo[(warp * 16 + rb) * D + col] = o[dt][2]; wo[(warp * 16 + rb) * D + col + 1] = o[dt][3];
     }
     __syncthreads();
+    // The spans that hold keys of this token (the others returned at the top).  n_spans * span_len short of the
+    // token's position: no block saw its last keys, and a softmax over a shortened context would look like a
+    // result; the rows are filled with NaN instead.
+    const int s_lo = lo / span_len;
+    int s_hi = pos / span_len;
+    const bool uncovered = s_hi >= n_spans;
+    if (uncovered) s_hi = n_spans - 1;
+    const bool alone = s_lo == s_hi;             // this block holds the whole context: its sums are the result
     for (int idx = tid; idx < gcount * D; idx += 128) {
         const int r = idx / D, col = idx - r * D;
         float mx = fmaxf(fmaxf(wm[r], wm[16 + r]), fmaxf(wm[32 + r], wm[48 + r]));
@@ -629,80 +638,86 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
             sum += f * wl[w * 16 + r];
         }
         const int head = kv_head * group + g0 + r;
+        if (alone) {
+            const float inv = sum > 0.f ? 1.f / sum : 0.f;
+            p.out[((size_t)n * p.n_q_heads + head) * D + col] =
+                __float2bfloat16_rn(uncovered ? __int_as_float(0x7fc00000) : acc * inv);
+            continue;
+        }
         const size_t slot = ((size_t)d_idx * p.n_q_heads + head) * n_spans + span;
         part_o[slot * D + col] = acc;
         if (col == 0) { part_ml[slot * 2] = mx; part_ml[slot * 2 + 1] = sum; }
     }
-}
+    if (alone) return;
 
-// ------------------------------------------------------------------ single tokens: merge of the spans
-__global__ void __launch_bounds__(128)
-attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, const float* __restrict__ part_o,
-                         const float* __restrict__ part_ml, int n_spans, int span_len_arg) {
-    // the step's description is older than the kernel before this one: read it while that one finishes
-    const int head = blockIdx.x, d_idx = blockIdx.y;
-    const int4 info = decode_info[d_idx];
-    const int n = info.x, pos = info.y;
-    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    const int span_len = span_len_arg > 0 ? span_len_arg : span_len_of(info.w, n_spans, -span_len_arg);
-    const int s_lo = lo / span_len;
-    int s_hi = pos / span_len;
-    // n_spans * span_len does not reach this token's position: the span kernel never saw its last keys, and a
-    // softmax over a shortened context would look like a result.  The row is filled with NaN instead.
-    const bool uncovered = s_hi >= n_spans;
-    if (uncovered) s_hi = n_spans - 1;
-    const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
-    qil_wait_for_producer();
-    qil_release_consumer();
-    // Spans are taken eight at a time: their (max, sum) pairs and this thread's columns of their partial
-    // outputs are all asked for before any is used, so a batch costs one trip to L2 instead of one for the
-    // maxima and another for the outputs; batches are folded into the running result as in the kernels above
-    // (rescale by exp2(old max - new max)).  The order of the sums is fixed by the span numbers.
-    constexpr int COLS = (D + 127) / 128, BATCH = 8;
-    float mx = -INFINITY, sum = 0.f;
-    float acc[COLS];
-#pragma unroll
-    for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
-    for (int s0 = s_lo; s0 <= s_hi; s0 += BATCH) {
-        float m[BATCH], l[BATCH], o[BATCH][COLS];
-#pragma unroll
-        for (int j = 0; j < BATCH; ++j) {
-            const bool live = s0 + j <= s_hi;
-            const size_t slot = base + (live ? s0 + j : s_lo);
-            const float2 ml = *reinterpret_cast<const float2*>(part_ml + slot * 2);
-            m[j] = live ? ml.x : -INFINITY;
-            l[j] = ml.y;
-#pragma unroll
-            for (int i = 0; i < COLS; ++i) {
-                const int col = threadIdx.x + i * 128;
-                o[j][i] = col < D ? part_o[slot * D + col] : 0.f;
-            }
-        }
-        float batch_max = m[0];
-#pragma unroll
-        for (int j = 1; j < BATCH; ++j) batch_max = fmaxf(batch_max, m[j]);
-        const float new_max = fmaxf(mx, batch_max);
-        const float ms = (new_max == -INFINITY) ? 0.f : new_max;
-        const float keep = exp2f(mx - ms);               // 0 for the first batch (mx = -inf)
-        sum *= keep;
-#pragma unroll
-        for (int i = 0; i < COLS; ++i) acc[i] *= keep;
-#pragma unroll
-        for (int j = 0; j < BATCH; ++j) {
-            const float f = exp2f(m[j] - ms);            // 0 for a slot past the last span
-            sum += f * l[j];
-#pragma unroll
-            for (int i = 0; i < COLS; ++i) acc[i] += f * o[j][i];
-        }
-        mx = new_max;
+    // ---- the merge of the spans, by whichever block of this (token, kv head, head chunk) finishes last.
+    // Every block that got this far takes a ticket after its partial results are in L2; the one that draws
+    // the last ticket reads all of them back and writes the output rows, and puts the ticket counter back to
+    // zero for the next launch.  The order of the sums is fixed by the span numbers, not by who merges.
+    __shared__ int merges;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned* ticket = tickets + (size_t)d_idx * gridDim.x + blockIdx.x;
+        const unsigned drawn = atomicAdd(ticket, 1u);
+        merges = drawn == (unsigned)(s_hi - s_lo);
+        if (merges) *ticket = 0u;
     }
-    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    __syncthreads();
+    if (!merges) return;
+    __threadfence();
+    // A warp per head.  Spans are taken eight at a time: their (max, sum) pairs and this lane's columns of
+    // their partial outputs are all asked for before any is used, so a batch costs one trip to L2; batches
+    // are folded into the running result as in the loops above (rescale by exp2(old max - new max)).
+    constexpr int COLS = (D + 31) / 32, BATCH = 8;
+    for (int r = warp; r < gcount; r += 4) {
+        const int head = kv_head * group + g0 + r;
+        const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
+        float mx = -INFINITY, sum = 0.f;
+        float acc[COLS];
 #pragma unroll
-    for (int i = 0; i < (D + 127) / 128; ++i) {
-        const int col = threadIdx.x + i * 128;
-        if (col < D)
-            p.out[((size_t)n * p.n_q_heads + head) * D + col] =
-                __float2bfloat16_rn(uncovered ? __int_as_float(0x7fc00000) : acc[i] * inv);
+        for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
+        for (int s0 = s_lo; s0 <= s_hi; s0 += BATCH) {
+            float m[BATCH], l[BATCH], o_part[BATCH][COLS];
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                const bool live = s0 + j <= s_hi;
+                const size_t slot = base + (live ? s0 + j : s_lo);
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + slot * 2));
+                m[j] = live ? ml.x : -INFINITY;
+                l[j] = ml.y;
+#pragma unroll
+                for (int i = 0; i < COLS; ++i) {
+                    const int col = lane + i * 32;
+                    o_part[j][i] = col < D ? __ldcg(part_o + slot * D + col) : 0.f;
+                }
+            }
+            float batch_max = m[0];
+#pragma unroll
+            for (int j = 1; j < BATCH; ++j) batch_max = fmaxf(batch_max, m[j]);
+            const float new_max = fmaxf(mx, batch_max);
+            const float ms = (new_max == -INFINITY) ? 0.f : new_max;
+            const float keep = exp2f(mx - ms);               // 0 for the first batch (mx = -inf)
+            sum *= keep;
+#pragma unroll
+            for (int i = 0; i < COLS; ++i) acc[i] *= keep;
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                const float f = exp2f(m[j] - ms);            // 0 for a slot past the last span
+                sum += f * l[j];
+#pragma unroll
+                for (int i = 0; i < COLS; ++i) acc[i] += f * o_part[j][i];
+            }
+            mx = new_max;
+        }
+        const float inv = sum > 0.f ? 1.f / sum : 0.f;
+#pragma unroll
+        for (int i = 0; i < COLS; ++i) {
+            const int col = lane + i * 32;
+            if (col < D)
+                p.out[((size_t)n * p.n_q_heads + head) * D + col] =
+                    __float2bfloat16_rn(uncovered ? __int_as_float(0x7fc00000) : acc[i] * inv);
+        }
     }
 }
 
@@ -783,13 +798,15 @@ extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const 
 }
 
 // decode_info: int32 [n_decode, 4] = (token, its absolute position, block-table row, 0).
-// Scratch: part_o needs n_decode * Hq * n_spans * D floats, part_ml n_decode * Hq * n_spans * 2 floats.
+// Scratch: part_o needs n_decode * Hq * n_spans * D floats, part_ml n_decode * Hq * n_spans * 2 floats, tickets
+// n_decode * n_kv_heads * ceil(Hq / n_kv_heads / 16) unsigned ints that are zero before the first launch (every
+// launch leaves them zero again).
 // n_spans * span_len must cover the longest context of the batch (max position + 1).
 // A negative span_len leaves the length to the kernels (see span_len_of): the fourth int of every decode_info
 // entry must then hold the step's longest context, and -span_len is the longest span that may come of it
 // (n_spans * -span_len covers the longest context the launch, or a graph recorded from it, will ever see).
 static int launch_decode(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
-                         float* part_o, float* part_ml, int n_spans, int span_len,
+                         float* part_o, float* part_ml, unsigned* tickets, int n_spans, int span_len,
                          const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                          int page_size, int num_pages, int window, float scale, const DecodeTail& tail,
                          cudaStream_t stream) {
@@ -798,29 +815,24 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
     if (check_decode_span(span_len, n_spans)) return -1;
-    if (part_o == nullptr || part_ml == nullptr) QIL_REFUSE("attention: decode needs scratch for %d spans", n_spans);
+    if (part_o == nullptr || part_ml == nullptr || tickets == nullptr)
+        QIL_REFUSE("attention: decode needs scratch for %d spans and its ticket counters", n_spans);
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention: decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
     if (n_decode > 65535 || n_spans > 65535) QIL_REFUSE("attention: grid too large");
     const int smem = decode_smem_bytes(span_len > 0 ? span_len : -span_len, page_size);
     if (ensure_decode_smem(attn_decode_span_kernel, smem)) return -1;
     qil_launch_chained(attn_decode_span_kernel, dim3(n_kv_heads * chunks, n_decode, n_spans), dim3(128), smem, stream,
-                       p, (const int4*)decode_info, part_o, part_ml, n_spans, span_len, tail);
-    {
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }
-    }
-    qil_launch_chained(attn_decode_merge_kernel, dim3(n_q_heads, n_decode), dim3(128), 0, stream,
-                       p, (const int4*)decode_info, (const float*)part_o, (const float*)part_ml, n_spans, span_len);
+                       p, (const int4*)decode_info, part_o, part_ml, tickets, n_spans, span_len, tail);
     QIL_CHECK_LAUNCH();
 }
 
 extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
-                               float* part_o, float* part_ml, int n_spans, int span_len,
+                               float* part_o, float* part_ml, unsigned* tickets, int n_spans, int span_len,
                                const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                                int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
     DecodeTail none = {};
-    return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
+    return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
                          table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, none, stream);
 }
 
@@ -831,7 +843,7 @@ extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const i
 // q_norm, k_norm bfloat16 [D] or null; rope float32 [rope_rows, rotary_dim] or null, rotary_dim a multiple
 // of 4.  At most 16 query heads per kv head.
 extern "C" int qil_attn_decode_qkv(const void* qkv, void* kv, void* out, const int* decode_info, int n_decode,
-                                   float* part_o, float* part_ml, int n_spans, int span_len,
+                                   float* part_o, float* part_ml, unsigned* tickets, int n_spans, int span_len,
                                    const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                                    int own_kv_heads, int page_size, int num_pages, int window, float scale,
                                    const void* q_norm, const void* k_norm, float eps, const float* rope,
@@ -848,6 +860,6 @@ extern "C" int qil_attn_decode_qkv(const void* qkv, void* kv, void* out, const i
     tail.qkv = (const bf16*)qkv; tail.q_norm = (const bf16*)q_norm; tail.k_norm = (const bf16*)k_norm;
     tail.rope = rope; tail.kv_out = (bf16*)kv; tail.eps = eps; tail.rotary_dim = rope ? rotary_dim : 0;
     tail.rope_rows = rope_rows; tail.own_kv_heads = own_kv_heads;
-    return launch_decode(qkv, kv, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
+    return launch_decode(qkv, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
                          table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, tail, stream);
 }

@@ -155,7 +155,8 @@ def choose_span(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> i
 
 
 def decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim):
-    """Partial sums and their (max, sum) pairs for the single-token kernel.
+    """Partial sums, their (max, sum) pairs and the ticket counters for the single-token kernel (the blocks
+    of a token's spans count themselves in, the last one merges; the counters are zero between launches).
 
     One pair of buffers per runner, kept in ``ctx.extras`` (which the runner carries from step to
     step) and replaced by a larger pair when a step needs more; a recorded graph keeps the pair it
@@ -163,11 +164,14 @@ def decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim):
     """
     slots = n_decode * n_q_heads * n_spans
     scratch = ctx.extras.get("attn_decode_scratch")
-    if scratch is None or scratch[0].numel() < slots * head_dim or scratch[1].numel() < slots * 2:
+    # one counter per (token, kv head, chunk of 16 query heads) at most: a counter per query head is always enough
+    if scratch is None or scratch[0].numel() < slots * head_dim or scratch[1].numel() < slots * 2 \
+            or len(scratch) < 3 or scratch[2].numel() < n_decode * n_q_heads:
         grow = lambda old, need: max(need, 2 * old.numel() if old is not None else 0)
-        old = scratch or (None, None)
+        old = (tuple(scratch) + (None, None, None))[:3] if scratch else (None, None, None)
         scratch = (torch.empty(grow(old[0], slots * head_dim), dtype=torch.float32, device=ctx.device),
-                   torch.empty(grow(old[1], slots * 2), dtype=torch.float32, device=ctx.device))
+                   torch.empty(grow(old[1], slots * 2), dtype=torch.float32, device=ctx.device),
+                   torch.zeros(grow(old[2], n_decode * n_q_heads), dtype=torch.int32, device=ctx.device))
         ctx.extras["attn_decode_scratch"] = scratch
     return scratch
 
@@ -183,16 +187,19 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
 
 
 def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
-           n_q_heads, n_kv_heads, head_dim, page_size, window, scale):
+           n_q_heads, n_kv_heads, head_dim, page_size, window, scale, tickets=None):
     """decode_info int32 [n_decode * 4]: (token, its position, block-table row, the step's longest context)
     per single token.  A negative ``span_len``: the kernels cut the step's longest context into ``n_spans``
-    equal spans of at most ``-span_len`` positions (see ``plan_spans``)."""
+    equal spans of at most ``-span_len`` positions (see ``plan_spans``).  ``tickets``: int32 zeros, one per
+    (token, query head) or more (``decode_scratch``); made here when not given."""
     lib = library(head_dim)
+    if tickets is None:
+        tickets = torch.zeros(n_decode * n_q_heads, dtype=torch.int32, device=q.device)
     _check(lib, lib.qil_attn_decode(
-        _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), c_int(n_spans),
+        _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), _p(tickets), c_int(n_spans),
         c_int(span_len), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads),
         c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), _stream()),
-        "attention (single tokens)", kernels=2)
+        "attention (single tokens)")
 
 
 def projection_tail_usable(ctx, qkv, cache, n_q_heads, n_kv_heads, head_dim, rotary_dim, norm_weights) -> bool:
@@ -224,16 +231,16 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
     n_decode = counts["decode_info"] // 4
     n_spans, longest_span = plan_spans(n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
                                        getattr(ctx, "min_context", 0) or None)
-    part_o, part_ml = decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim)
+    part_o, part_ml, tickets = decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim)
     lib = library(head_dim)
     _check(lib, lib.qil_attn_decode_qkv(
         _p(qkv), _p(cache.pages), _p(out), _p(arrays["decode_info"]), c_int(n_decode), _p(part_o), _p(part_ml),
-        c_int(n_spans), c_int(-longest_span), _p(cache.block_table), c_int(cache.block_table.shape[1]),
+        _p(tickets), c_int(n_spans), c_int(-longest_span), _p(cache.block_table), c_int(cache.block_table.shape[1]),
         c_int(n_q_heads), c_int(n_kv_heads), c_int(own_kv_heads), c_int(cache.page_size),
         c_int(cache.pages.shape[0]), c_int(window), c_float(scale), _p(q_norm), _p(k_norm), c_float(float(eps)),
         _p(rope_table), c_int(rotary_dim if rope_table is not None else 0),
         c_int(rope_table.shape[0] if rope_table is not None else 0), _stream()),
-        "attention (single tokens from the projection)", kernels=2)
+        "attention (single tokens from the projection)")
 
 
 def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
@@ -258,6 +265,6 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
     if n_decode:
         n_spans, longest_span = plan_spans(n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
                                            getattr(ctx, "min_context", 0) or None)
-        part_o, part_ml = decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim)
+        part_o, part_ml, tickets = decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim)
         decode(q, cache.pages, out, arrays["decode_info"], n_decode, part_o, part_ml, n_spans, -longest_span,
-               cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale)
+               cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale, tickets)

@@ -314,7 +314,8 @@ def test_attention_single_tokens_from_the_projection(n_q, n_kv, d, lengths, page
                                count=dict(decode_info=4 * n, tile_info=0, big_tile_info=0, rest_tile_info=0))
         ctx = SimpleNamespace(n_tokens=n, max_context=bound, min_context=longest,
                               plans={attention_mma.PLAN_KEY: plan},
-                              extras={"attn_decode_scratch": (part_o, part_ml)}, device=qkv.device)
+                              extras={"attn_decode_scratch": (part_o, part_ml, torch.zeros(n * n_q, dtype=torch.int32).cuda())},
+                              device=qkv.device)
         cache = SimpleNamespace(pages=pages_b, block_table=table.cuda(), page_size=page)
         assert attention_mma.projection_tail_usable(ctx, qkv, cache, n_q, n_kv, d, rotary, (q_norm, k_norm))
         attention_mma.attend_projection(ctx, qkv, cache, out_b, n_q, n_kv, own_kv, d, window, d ** -0.5, q_norm,

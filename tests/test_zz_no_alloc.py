@@ -104,15 +104,17 @@ def test_the_two_entry_points_of_one_library_share_the_kernels_shared_memory_lim
     slots = n * short["n_q"] * short["n_spans"]
     part_o = torch.empty(slots * HEAD_DIM, dtype=torch.float32, device="cuda")
     part_ml = torch.empty(slots * 2, dtype=torch.float32, device="cuda")
+    tickets = torch.zeros(n * short["n_q"], dtype=torch.int32, device="cuda")
     out = torch.full_like(short["q"], float("nan"))
     ptr = lambda t: c_void_p(t.data_ptr())
     code = lib.qil_attn_decode(
         ptr(short["q"]), ptr(short["pool"]), ptr(out), ptr(short["decode_info"]), c_int(n), ptr(part_o), ptr(part_ml),
-        c_int(short["n_spans"]), c_int(short["span_len"]), ptr(short["table"]), c_int(short["table"].shape[1]),
+        ptr(tickets), c_int(short["n_spans"]), c_int(short["span_len"]), ptr(short["table"]), c_int(short["table"].shape[1]),
         c_int(short["n_q"]), c_int(short["n_kv"]), c_int(short["page"]), c_int(short["pool"].shape[0]), c_int(0),
         c_float(HEAD_DIM ** -0.5), c_void_p(torch.cuda.current_stream().cuda_stream))
     assert code == 0, lib.qil_last_error().decode()
     torch.testing.assert_close(out.float().cpu(), short["expected"].float(), atol=8e-3 * 2, rtol=8e-3)
+    assert int(tickets.sum()) == 0               # the kernel leaves its counters at zero
     long = decode_case([2000, 5], n_q=8, n_kv=2, page=4, seed=44, span_len=2048)     # many more page ids per span
     code, got = no_alloc(lib, long)
     torch.cuda.synchronize()
