@@ -398,11 +398,17 @@ __device__ __forceinline__ void warp_norm_rotate_head(const bf16* __restrict__ s
 // ------------------------------------------------------------------ single tokens: spans
 // decode_info: (token in the flat batch, its absolute position, block-table row, unused) per token.
 // part_o  [n_decode, Hq, n_spans, D] float32, unnormalised; part_ml [n_decode, Hq, n_spans, 2] (max, sum).
-__global__ void __launch_bounds__(128)
-attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, unsigned* __restrict__ tickets, int n_spans, int span_len_arg,
-                        DecodeTail tail) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+//
+// The work of one block, as a function of its place in the grid (``block_x`` of ``grid_x``, ``d_idx``, ``span``)
+// so that a kernel that walks several such places in a loop can call it too.  ``wait_for_inputs`` is called once,
+// after the first key and value tiles have been asked for: up to there only memory that nothing of this step
+// writes is read.
+template <typename Wait>
+__device__ __forceinline__ void attn_decode_span_block(
+        const AttnParams& p, const int4* __restrict__ decode_info, float* __restrict__ part_o,
+        float* __restrict__ part_ml, unsigned* __restrict__ tickets, int n_spans, int span_len_arg,
+        const DecodeTail& tail, unsigned char* smem_raw, int block_x, int grid_x, int d_idx, int span,
+        Wait wait_for_inputs) {
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);      // [16][LDS]
     bf16* sK = sQ + 16 * LDS;                           // [2][64][LDS]
     bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
@@ -412,9 +418,8 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = p.n_q_heads / p.n_kv_heads;
     const int chunks = (group + 15) / 16;
-    const int kv_head = blockIdx.x / chunks, g0 = (blockIdx.x % chunks) * 16;
+    const int kv_head = block_x / chunks, g0 = (block_x % chunks) * 16;
     const int gcount = min(16, group - g0);
-    const int span = blockIdx.z, d_idx = blockIdx.y;     // the span index varies slowest: see span_len_of
     const int4 info = decode_info[d_idx];
     const int n = info.x, pos = info.y;
     const int hi = pos;
@@ -464,8 +469,7 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     cp_async_commit();
     if (early) issue_rows(off0, my_v, v_plane);
     cp_async_commit();
-    qil_wait_for_producer();
-    qil_release_consumer();
+    wait_for_inputs();
     if (tail.qkv == nullptr) {   // finished queries: the heads of this kv head, 8 threads per row
         const int row = tid >> 3;
         const bool valid = row < gcount;
@@ -658,7 +662,7 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        unsigned* ticket = tickets + (size_t)d_idx * gridDim.x + blockIdx.x;
+        unsigned* ticket = tickets + (size_t)d_idx * grid_x + block_x;
         const unsigned drawn = atomicAdd(ticket, 1u);
         merges = drawn == (unsigned)(s_hi - s_lo);
         if (merges) *ticket = 0u;
@@ -719,6 +723,17 @@ attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, floa
                     __float2bfloat16_rn(uncovered ? __int_as_float(0x7fc00000) : acc[i] * inv);
         }
     }
+}
+
+__global__ void __launch_bounds__(128)
+attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, unsigned* __restrict__ tickets, int n_spans, int span_len_arg,
+                        DecodeTail tail) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    // the span index varies slowest: see span_len_of
+    attn_decode_span_block(p, decode_info, part_o, part_ml, tickets, n_spans, span_len_arg, tail, smem_raw,
+                           (int)blockIdx.x, (int)gridDim.x, (int)blockIdx.y, (int)blockIdx.z,
+                           [] { qil_wait_for_producer(); qil_release_consumer(); });
 }
 
 // ------------------------------------------------------------------ entry points

@@ -137,15 +137,16 @@ def _plan_tiles(blocks_per_span, slots, lo, hi) -> int:
     return best
 
 
-def plan_spans(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128, min_context=None):
+def plan_spans(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128, min_context=None, slots=None):
     """(n_spans, longest span) for steps whose longest context lies in [min_context, max_context]: the kernels
     cut each step's own longest context into ``n_spans`` equal spans (a recorded graph is replayed while
     contexts grow), so the count is chosen for both ends of the range; the longest span sizes shared memory.
-    Eager steps ask once per layer and step: the answer is remembered per (blocks, tiles)."""
+    Eager steps ask once per layer and step: the answer is remembered per (blocks, tiles).  ``slots``: how many
+    blocks run at a time, when it is not this module's span kernel that runs them."""
     blocks_per_span = n_decode * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16)
     hi = max(1, (max_context + KV_TILE - 1) // KV_TILE)
     lo = max(1, min(hi, ((min_context or max_context) + KV_TILE - 1) // KV_TILE))
-    n_spans = _plan_tiles(blocks_per_span, _slots(head_dim), lo, hi)
+    n_spans = _plan_tiles(blocks_per_span, slots or _slots(head_dim), lo, hi)
     return n_spans, -(-hi // n_spans) * KV_TILE
 
 
