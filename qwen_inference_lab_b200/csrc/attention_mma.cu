@@ -395,6 +395,62 @@ __device__ __forceinline__ void warp_norm_rotate_head(const bf16* __restrict__ s
     }
 }
 
+// The spans of one (token, query head) folded into its output row, by one warp.  Spans are taken eight at a
+// time: their (max, sum) pairs and this lane's columns of their partial outputs are all asked for before any is
+// used, so a batch costs one trip to L2; batches are folded into the running result as in the loops of the
+// kernels (rescale by exp2(old max - new max)).  The order of the sums is fixed by the span numbers.
+__device__ __forceinline__ void merge_spans_of_head(const AttnParams& p, const float* __restrict__ part_o,
+                                                    const float* __restrict__ part_ml, int d_idx, int n, int head,
+                                                    int n_spans, int s_lo, int s_hi, bool uncovered, int lane) {
+    constexpr int COLS = (D + 31) / 32, BATCH = 8;
+    const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
+    float mx = -INFINITY, sum = 0.f;
+    float acc[COLS];
+#pragma unroll
+    for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
+    for (int s0 = s_lo; s0 <= s_hi; s0 += BATCH) {
+        float m[BATCH], l[BATCH], o_part[BATCH][COLS];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+            const bool live = s0 + j <= s_hi;
+            const size_t slot = base + (live ? s0 + j : s_lo);
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + slot * 2));
+            m[j] = live ? ml.x : -INFINITY;
+            l[j] = ml.y;
+#pragma unroll
+            for (int i = 0; i < COLS; ++i) {
+                const int col = lane + i * 32;
+                o_part[j][i] = col < D ? __ldcg(part_o + slot * D + col) : 0.f;
+            }
+        }
+        float batch_max = m[0];
+#pragma unroll
+        for (int j = 1; j < BATCH; ++j) batch_max = fmaxf(batch_max, m[j]);
+        const float new_max = fmaxf(mx, batch_max);
+        const float ms = (new_max == -INFINITY) ? 0.f : new_max;
+        const float keep = exp2f(mx - ms);               // 0 for the first batch (mx = -inf)
+        sum *= keep;
+#pragma unroll
+        for (int i = 0; i < COLS; ++i) acc[i] *= keep;
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+            const float f = exp2f(m[j] - ms);            // 0 for a slot past the last span
+            sum += f * l[j];
+#pragma unroll
+            for (int i = 0; i < COLS; ++i) acc[i] += f * o_part[j][i];
+        }
+        mx = new_max;
+    }
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+#pragma unroll
+    for (int i = 0; i < COLS; ++i) {
+        const int col = lane + i * 32;
+        if (col < D)
+            p.out[((size_t)n * p.n_q_heads + head) * D + col] =
+                __float2bfloat16_rn(uncovered ? __int_as_float(0x7fc00000) : acc[i] * inv);
+    }
+}
+
 // ------------------------------------------------------------------ single tokens: spans
 // decode_info: (token in the flat batch, its absolute position, block-table row, unused) per token.
 // part_o  [n_decode, Hq, n_spans, D] float32, unnormalised; part_ml [n_decode, Hq, n_spans, 2] (max, sum).
@@ -652,77 +708,46 @@ __device__ __forceinline__ void attn_decode_span_block(
         part_o[slot * D + col] = acc;
         if (col == 0) { part_ml[slot * 2] = mx; part_ml[slot * 2 + 1] = sum; }
     }
-    if (alone) return;
+    if (alone || tickets == nullptr) return;        // no counters: a merge kernel follows
 
     // ---- the merge of the spans, by whichever block of this (token, kv head, head chunk) finishes last.
     // Every block that got this far takes a ticket after its partial results are in L2; the one that draws
     // the last ticket reads all of them back and writes the output rows, and puts the ticket counter back to
     // zero for the next launch.  The order of the sums is fixed by the span numbers, not by who merges.
     __shared__ int merges;
-    __threadfence();
-    __syncthreads();
+    __syncthreads();             // every thread's partial results are written ...
     if (tid == 0) {
+        __threadfence();         // ... and in L2 before the ticket is (one fence after the barrier covers them all)
         unsigned* ticket = tickets + (size_t)d_idx * grid_x + block_x;
         const unsigned drawn = atomicAdd(ticket, 1u);
         merges = drawn == (unsigned)(s_hi - s_lo);
-        if (merges) *ticket = 0u;
+        if (merges) { *ticket = 0u; __threadfence(); }      // the other blocks' results, read below from L2
     }
     __syncthreads();
     if (!merges) return;
-    __threadfence();
-    // A warp per head.  Spans are taken eight at a time: their (max, sum) pairs and this lane's columns of
-    // their partial outputs are all asked for before any is used, so a batch costs one trip to L2; batches
-    // are folded into the running result as in the loops above (rescale by exp2(old max - new max)).
-    constexpr int COLS = (D + 31) / 32, BATCH = 8;
-    for (int r = warp; r < gcount; r += 4) {
-        const int head = kv_head * group + g0 + r;
-        const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
-        float mx = -INFINITY, sum = 0.f;
-        float acc[COLS];
-#pragma unroll
-        for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
-        for (int s0 = s_lo; s0 <= s_hi; s0 += BATCH) {
-            float m[BATCH], l[BATCH], o_part[BATCH][COLS];
-#pragma unroll
-            for (int j = 0; j < BATCH; ++j) {
-                const bool live = s0 + j <= s_hi;
-                const size_t slot = base + (live ? s0 + j : s_lo);
-                const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + slot * 2));
-                m[j] = live ? ml.x : -INFINITY;
-                l[j] = ml.y;
-#pragma unroll
-                for (int i = 0; i < COLS; ++i) {
-                    const int col = lane + i * 32;
-                    o_part[j][i] = col < D ? __ldcg(part_o + slot * D + col) : 0.f;
-                }
-            }
-            float batch_max = m[0];
-#pragma unroll
-            for (int j = 1; j < BATCH; ++j) batch_max = fmaxf(batch_max, m[j]);
-            const float new_max = fmaxf(mx, batch_max);
-            const float ms = (new_max == -INFINITY) ? 0.f : new_max;
-            const float keep = exp2f(mx - ms);               // 0 for the first batch (mx = -inf)
-            sum *= keep;
-#pragma unroll
-            for (int i = 0; i < COLS; ++i) acc[i] *= keep;
-#pragma unroll
-            for (int j = 0; j < BATCH; ++j) {
-                const float f = exp2f(m[j] - ms);            // 0 for a slot past the last span
-                sum += f * l[j];
-#pragma unroll
-                for (int i = 0; i < COLS; ++i) acc[i] += f * o_part[j][i];
-            }
-            mx = new_max;
-        }
-        const float inv = sum > 0.f ? 1.f / sum : 0.f;
-#pragma unroll
-        for (int i = 0; i < COLS; ++i) {
-            const int col = lane + i * 32;
-            if (col < D)
-                p.out[((size_t)n * p.n_q_heads + head) * D + col] =
-                    __float2bfloat16_rn(uncovered ? __int_as_float(0x7fc00000) : acc[i] * inv);
-        }
-    }
+    for (int r = warp; r < gcount; r += 4)
+        merge_spans_of_head(p, part_o, part_ml, d_idx, n, kv_head * group + g0 + r, n_spans, s_lo, s_hi, uncovered, lane);
+}
+
+// The merge as a kernel of its own, for launches without ticket counters: a warp per (token, query head).
+__global__ void __launch_bounds__(128)
+attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, const float* __restrict__ part_o,
+                         const float* __restrict__ part_ml, int n_spans, int span_len_arg) {
+    // the step's description is older than the kernel before this one: read it while that one finishes
+    const int d_idx = blockIdx.y, head = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int4 info = decode_info[d_idx];
+    const int pos = info.y;
+    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int span_len = span_len_arg > 0 ? span_len_arg : span_len_of(info.w, n_spans, -span_len_arg);
+    const int s_lo = lo / span_len;
+    int s_hi = pos / span_len;
+    const bool uncovered = s_hi >= n_spans;
+    if (uncovered) s_hi = n_spans - 1;
+    qil_wait_for_producer();
+    qil_release_consumer();
+    if (s_lo == s_hi) return;       // one span held the whole context: its block wrote the rows itself
+    if (head < p.n_q_heads)
+        merge_spans_of_head(p, part_o, part_ml, d_idx, info.x, head, n_spans, s_lo, s_hi, uncovered, threadIdx.x & 31);
 }
 
 __global__ void __launch_bounds__(128)
@@ -815,7 +840,8 @@ extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const 
 // decode_info: int32 [n_decode, 4] = (token, its absolute position, block-table row, 0).
 // Scratch: part_o needs n_decode * Hq * n_spans * D floats, part_ml n_decode * Hq * n_spans * 2 floats, tickets
 // n_decode * n_kv_heads * ceil(Hq / n_kv_heads / 16) unsigned ints that are zero before the first launch (every
-// launch leaves them zero again).
+// launch leaves them zero again), or null: then a second kernel merges the spans (what many tokens want: a
+// ticket costs every block a fence and an atomic at its end, a merge kernel costs one launch).
 // n_spans * span_len must cover the longest context of the batch (max position + 1).
 // A negative span_len leaves the length to the kernels (see span_len_of): the fourth int of every decode_info
 // entry must then hold the step's longest context, and -span_len is the longest span that may come of it
@@ -830,8 +856,7 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
     if (check_decode_span(span_len, n_spans)) return -1;
-    if (part_o == nullptr || part_ml == nullptr || tickets == nullptr)
-        QIL_REFUSE("attention: decode needs scratch for %d spans and its ticket counters", n_spans);
+    if (part_o == nullptr || part_ml == nullptr) QIL_REFUSE("attention: decode needs scratch for %d spans", n_spans);
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention: decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
     if (n_decode > 65535 || n_spans > 65535) QIL_REFUSE("attention: grid too large");
@@ -839,6 +864,12 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
     if (ensure_decode_smem(attn_decode_span_kernel, smem)) return -1;
     qil_launch_chained(attn_decode_span_kernel, dim3(n_kv_heads * chunks, n_decode, n_spans), dim3(128), smem, stream,
                        p, (const int4*)decode_info, part_o, part_ml, tickets, n_spans, span_len, tail);
+    if (tickets == nullptr) {
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }
+        qil_launch_chained(attn_decode_merge_kernel, dim3((n_q_heads + 3) / 4, n_decode), dim3(128), 0, stream,
+                           p, (const int4*)decode_info, (const float*)part_o, (const float*)part_ml, n_spans, span_len);
+    }
     QIL_CHECK_LAUNCH();
 }
 

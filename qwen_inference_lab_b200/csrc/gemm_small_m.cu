@@ -37,6 +37,7 @@
 #define GSM_RUNS (GSM_STAGE_K / GSM_WARPS / 32)   // runs of 32 k-values per warp and stage
 #define GSM_STAGE_K 512                    // k-values per stage
 #define GSM_STAGES 4
+#define GSM_L2_AHEAD 2048                  // bytes of each weight row that a waiting block asks L2 for beyond its ring
 #define GSM_ROW_BYTES (GSM_STAGE_K * 2 + 64)   // row stride = 64 mod 128 bytes: 16-byte reads of 8 rows x 4 pieces hit every bank once
 #define GSM_STAGE_BYTES (GSM_ROWS * GSM_ROW_BYTES)
 
@@ -126,7 +127,7 @@ template <int NT, int NORM>
 __global__ void __launch_bounds__(GSM_WARPS * 32)
 gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const bf16* __restrict__ bias,
                     const bf16* residual, void* out, const bf16* __restrict__ norm_w, float norm_eps,
-                    int M, int N, int K, int out_f32, int silu_pairs) {
+                    int M, int N, int K, int out_f32, int silu_pairs, int first_wave) {
     extern __shared__ __align__(128) unsigned char ring[];          // [STAGES][STAGE_BYTES]
     constexpr int XROWS = 8 * NT;
     constexpr int NORM_ROW = GSM_ROWS + XROWS;                      // the stage row of the norm weight
@@ -158,6 +159,20 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
                                          s * GSM_STAGE_K, tid);
         }
         asm volatile("cp.async.commit_group;\n" ::);
+    }
+    // While a block of the first wave waits for the kernel before it, L2 can fetch a little more of its
+    // weight rows than the ring holds (lane r of warp 0 asks for the next GSM_L2_AHEAD bytes of row r), so the
+    // memory system has work while that kernel drains.  Measured on the Qwen3-8B decode step: 1 % of the step
+    // with 1 to 2 KB a row, nothing with 3 KB, a loss from 5 KB on and when later waves do it too.
+    if (warp == 0 && lane < GSM_ROWS && (int)blockIdx.x < first_wave && copy.short_path) {
+        const long long begin = (long long)(STAGES - 1) * GSM_STAGE_K * 2;
+        long long bytes = (long long)K * 2 - begin;
+        if (bytes > GSM_L2_AHEAD) bytes = GSM_L2_AHEAD;
+        bytes &= ~15ll;
+        if (bytes > 0) {
+            const char* row = reinterpret_cast<const char*>(W + (size_t)(n0 + lane) * K) + begin;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(row), "r"((unsigned)bytes) : "memory");
+        }
     }
     qil_wait_for_producer();
     qil_release_consumer();
@@ -297,7 +312,11 @@ extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, 
     const int smem1 = GSM_STAGES * (GSM_ROWS + 8) * GSM_ROW_BYTES, smem1n = GSM_STAGES * (GSM_ROWS + 8 + 1) * GSM_ROW_BYTES;
     const int smem2 = 3 * (GSM_ROWS + 16) * GSM_ROW_BYTES, smem2n = 3 * (GSM_ROWS + 16 + 1) * GSM_ROW_BYTES;
     static bool configured = false;
+    static int first_wave = 0;          // blocks that run at once: two a multiprocessor
     if (!configured) {
+        int device = 0, sms = 0;
+        if (cudaGetDevice(&device) == cudaSuccess &&
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess) first_wave = 2 * sms;
         cudaError_t e[4] = {
             cudaFuncSetAttribute(gemm_small_m_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1),
             cudaFuncSetAttribute(gemm_small_m_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2),
@@ -310,7 +329,7 @@ extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, 
 #define GSM_LAUNCH(NT, NORM, SMEM)                                                                                  \
     qil_launch_chained(gemm_small_m_kernel<NT, NORM>, dim3(blocks), dim3(GSM_WARPS * 32), SMEM, stream,           \
                        (const bf16*)x, (const bf16*)W, (const bf16*)bias, (const bf16*)residual, out,                \
-                       (const bf16*)norm_w, norm_eps, M, N, K, out_f32, silu_pairs)
+                       (const bf16*)norm_w, norm_eps, M, N, K, out_f32, silu_pairs, first_wave)
     if (norm_w == nullptr) {
         if (M <= 8) GSM_LAUNCH(1, 0, smem1); else GSM_LAUNCH(2, 0, smem2);
     } else {

@@ -155,6 +155,16 @@ def choose_span(n_decode, n_q_heads, n_kv_heads, max_context, head_dim=128) -> i
     return plan_spans(n_decode, n_q_heads, n_kv_heads, max_context, head_dim)[1]
 
 
+def merge_in_kernel(n_decode, n_q_heads, n_kv_heads, head_dim) -> bool:
+    """Should the span kernel's blocks merge their spans themselves (the last block of a token's spans, found
+    by a ticket counter) instead of leaving it to a second kernel?  A ticket costs every block a fence and an
+    atomic at its end; a merge kernel costs a launch between the attention and the output projection.  With
+    few tokens the launch is what shows, with many (a span's worth of blocks fills the GPU) the tickets are."""
+    import os
+    blocks_per_span = n_decode * n_kv_heads * ((n_q_heads // n_kv_heads + 15) // 16)
+    return blocks_per_span <= int(os.environ.get("QIL_TICKET_MAX_BLOCKS", _slots(head_dim)))
+
+
 def decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim):
     """Partial sums, their (max, sum) pairs and the ticket counters for the single-token kernel (the blocks
     of a token's spans count themselves in, the last one merges; the counters are zero between launches).
@@ -192,15 +202,14 @@ def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_
     """decode_info int32 [n_decode * 4]: (token, its position, block-table row, the step's longest context)
     per single token.  A negative ``span_len``: the kernels cut the step's longest context into ``n_spans``
     equal spans of at most ``-span_len`` positions (see ``plan_spans``).  ``tickets``: int32 zeros, one per
-    (token, query head) or more (``decode_scratch``); made here when not given."""
+    (token, query head) or more (``decode_scratch``): the last block of a token's spans merges them; None: a
+    second kernel does."""
     lib = library(head_dim)
-    if tickets is None:
-        tickets = torch.zeros(n_decode * n_q_heads, dtype=torch.int32, device=q.device)
     _check(lib, lib.qil_attn_decode(
         _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), _p(tickets), c_int(n_spans),
         c_int(span_len), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads),
         c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), _stream()),
-        "attention (single tokens)")
+        "attention (single tokens)", kernels=1 if tickets is not None else 2)
 
 
 def projection_tail_usable(ctx, qkv, cache, n_q_heads, n_kv_heads, head_dim, rotary_dim, norm_weights) -> bool:
@@ -233,6 +242,8 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
     n_spans, longest_span = plan_spans(n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
                                        getattr(ctx, "min_context", 0) or None)
     part_o, part_ml, tickets = decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim)
+    if not merge_in_kernel(n_decode, n_q_heads, n_kv_heads, head_dim):
+        tickets = None
     lib = library(head_dim)
     _check(lib, lib.qil_attn_decode_qkv(
         _p(qkv), _p(cache.pages), _p(out), _p(arrays["decode_info"]), c_int(n_decode), _p(part_o), _p(part_ml),
@@ -241,7 +252,7 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
         c_int(cache.pages.shape[0]), c_int(window), c_float(scale), _p(q_norm), _p(k_norm), c_float(float(eps)),
         _p(rope_table), c_int(rotary_dim if rope_table is not None else 0),
         c_int(rope_table.shape[0] if rope_table is not None else 0), _stream()),
-        "attention (single tokens from the projection)")
+        "attention (single tokens from the projection)", kernels=1 if tickets is not None else 2)
 
 
 def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
@@ -267,5 +278,7 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
         n_spans, longest_span = plan_spans(n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
                                            getattr(ctx, "min_context", 0) or None)
         part_o, part_ml, tickets = decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim)
+        if not merge_in_kernel(n_decode, n_q_heads, n_kv_heads, head_dim):
+            tickets = None
         decode(q, cache.pages, out, arrays["decode_info"], n_decode, part_o, part_ml, n_spans, -longest_span,
                cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale, tickets)

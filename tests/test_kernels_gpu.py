@@ -209,7 +209,7 @@ def test_attention_generic(dtype, case):
     close(out, expected, dtype, scale=2)
 
 
-def run_mma(q, pool, table, meta, n_q, n_kv, d, page, window, span_len=256):
+def run_mma(q, pool, table, meta, n_q, n_kv, d, page, window, span_len=256, tickets=False):
     from qwen_inference_lab_b200.kernels import attention_mma
     as_int = lambda values: torch.tensor(values, dtype=torch.int32).cuda()
     tile_info, decode_info = [], []
@@ -235,8 +235,11 @@ def run_mma(q, pool, table, meta, n_q, n_kv, d, page, window, span_len=256):
             n_spans = (longest + span_len - 1) // span_len + 1   # one spare span
         part_o = torch.full((n_decode * n_q * n_spans * d,), float("nan"), dtype=torch.float32).cuda()
         part_ml = torch.full((n_decode * n_q * n_spans * 2,), float("nan"), dtype=torch.float32).cuda()
+        counters = torch.zeros(n_decode * n_q, dtype=torch.int32).cuda() if tickets else None
         attention_mma.decode(qg, pg, out, as_int(decode_info), n_decode, part_o, part_ml, n_spans, span_len,
-                             table.cuda(), n_q, n_kv, d, page, window, d ** -0.5)
+                             table.cuda(), n_q, n_kv, d, page, window, d ** -0.5, tickets=counters)
+        if tickets:
+            assert int(counters.sum()) == 0            # the last block of every token's spans put its counter back
     return out
 
 
@@ -262,6 +265,11 @@ def test_attention_tensor_core(case):
     for span_len in (64, 256, 2048, 0):
         out = run_mma(last_q, pool, table, last_meta, n_q, n_kv, d, page, window, span_len=span_len)
         close(out, last_expected, torch.bfloat16, scale=2)
+        # the spans merged by the span kernel's own last blocks (ticket counters) instead of a second kernel:
+        # the same sums in the same order, so the same bits
+        merged_in_kernel = run_mma(last_q, pool, table, last_meta, n_q, n_kv, d, page, window, span_len=span_len,
+                                   tickets=True)
+        assert torch.equal(out, merged_in_kernel)
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,lengths,page,window,rotary,norms,own", [
