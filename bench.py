@@ -304,7 +304,10 @@ def mixed_workload(bench, requests=64, new_tokens=128, longest=2048, seed=4):
     pages = sum((n + new_tokens + PAGE_SIZE - 1) // PAGE_SIZE + 1 for n in lengths)
     engine = Engine(bench.model, num_pages=pages, page_size=PAGE_SIZE, token_budget=4096, prefill_chunk=2048,
                     max_active=requests)
-    engine.generate(prompts[:2], max_new_tokens=4, ignore_eos=True)        # set-up outside the timed run
+    # set-up outside the timed run, as the reference's harness keeps load and warm-up out of its samples
+    # (docs/batched-gpu-validation-2026-09-20.md:19-24): the same workload once, which also records the decode
+    # steps' graphs for the batch sizes and context ranges it passes through
+    engine.generate(prompts, max_new_tokens=new_tokens, ignore_eos=True)
     torch.cuda.synchronize()
     steps_before = engine.runner.steps_run
     begin = time.perf_counter()

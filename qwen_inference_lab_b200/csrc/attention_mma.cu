@@ -395,14 +395,14 @@ __device__ __forceinline__ void warp_norm_rotate_head(const bf16* __restrict__ s
     }
 }
 
-// The spans of one (token, query head) folded into its output row, by one warp.  Spans are taken eight at a
+// The spans of one (token, query head) folded into its output row, by one warp.  Spans are taken sixteen at a
 // time: their (max, sum) pairs and this lane's columns of their partial outputs are all asked for before any is
 // used, so a batch costs one trip to L2; batches are folded into the running result as in the loops of the
 // kernels (rescale by exp2(old max - new max)).  The order of the sums is fixed by the span numbers.
 __device__ __forceinline__ void merge_spans_of_head(const AttnParams& p, const float* __restrict__ part_o,
                                                     const float* __restrict__ part_ml, int d_idx, int n, int head,
                                                     int n_spans, int s_lo, int s_hi, bool uncovered, int lane) {
-    constexpr int COLS = (D + 31) / 32, BATCH = 8;
+    constexpr int COLS = (D + 31) / 32, BATCH = 16;
     const size_t base = ((size_t)d_idx * p.n_q_heads + head) * n_spans;
     float mx = -INFINITY, sum = 0.f;
     float acc[COLS];
