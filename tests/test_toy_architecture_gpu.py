@@ -192,16 +192,18 @@ def build_toy(config):
 
 
 # ------------------------------------------------------------------ the toy, written plainly for whole sequences
-def toy_plain_logits(tokens, w, c: ToyConfig):
+def toy_plain_logits(tokens, w, c: ToyConfig, dtype=torch.float32):
+    """``dtype``: the activation dtype; the state mixer and the routed feed-forward compute in float32 and round
+    their sum with the residual once, as the toy's parts above do."""
     T = len(tokens)
-    x = w["embed.weight"][torch.as_tensor(tokens)]
+    x = w["embed.weight"].to(dtype)[torch.as_tensor(tokens)]
     positions = torch.arange(T)
     kv_of_layer1 = {}
 
     def routed_ff(i, x):
-        n = plain.rms_norm(x, w[f"blocks.{i}.norm_b.weight"], c.eps)
+        n = plain.rms_norm(x, w[f"blocks.{i}.norm_b.weight"], c.eps).float()
         logits = n @ w[f"blocks.{i}.ff.router"].t()
-        out = torch.zeros_like(x)
+        out = torch.zeros(x.shape)
         for t in range(T):                      # one token at a time: the plainest form
             top, chosen = logits[t].topk(c.experts_per_token)
             share = torch.softmax(top, dim=-1)
@@ -209,7 +211,7 @@ def toy_plain_logits(tokens, w, c: ToyConfig):
                 pre = f"blocks.{i}.ff.experts.{e}."
                 hidden = torch.nn.functional.silu(n[t] @ w[pre + "gate"].t()) * (n[t] @ w[pre + "up"].t())
                 out[t] += p * (hidden @ w[pre + "down"].t())
-        return x + out
+        return (x.float() + out).to(x.dtype)
 
     def ff(i, x):
         if i == 2:
@@ -219,13 +221,14 @@ def toy_plain_logits(tokens, w, c: ToyConfig):
         return x + plain.linear(gate * plain.linear(n, w[f"blocks.{i}.ff.up.weight"]), w[f"blocks.{i}.ff.down.weight"])
 
     def state_layer(x):
-        n = plain.rms_norm(x, w["blocks.0.norm_a.weight"], c.eps)
+        n = plain.rms_norm(x, w["blocks.0.norm_a.weight"], c.eps).float()
         u = n @ w["blocks.0.state.w_in"].t()
         h, rows = torch.zeros(c.state_width), []
         for t in range(T):
             h = c.decay * h + u[t]
             rows.append(h)
-        return ff(0, x + torch.stack(rows) @ w["blocks.0.state.w_out"].t())
+        mixed = (torch.stack(rows) @ w["blocks.0.state.w_out"].t()).to(x.dtype)
+        return ff(0, (x.float() + mixed.float()).to(x.dtype))
 
     def rotate_part(v, rotary_dim):
         angles = plain.rotary_angles(positions, rotary_dim, c.theta) if rotary_dim == c.head_dim else \
@@ -331,13 +334,14 @@ def test_window_group_holds_few_pages_while_a_long_request_runs(toy):
     cache.check_invariants()
 
 
-def test_toy_in_bfloat16_agrees_with_itself_across_cuts(toy):
+def test_toy_in_bfloat16_under_two_cuts(toy):
+    """bfloat16: whole and in portions, judged like the replay tests: against the plain float32 rows with the plain
+    form's own bfloat16 arithmetic as the yardstick, and by the best token where it is clear."""
     config, folder, weights = toy
     requests = {"a": torch.randint(0, config.vocab_size, (70,), generator=torch.Generator().manual_seed(3)).tolist()}
     model, cache, runner = engine_parts(folder, torch.bfloat16)
-    whole = harness.run_schedule(runner, cache, harness.whole_schedule(requests))
-    cut = harness.run_schedule(runner, cache, harness.chunk_schedule(requests))
-    truth = toy_plain_logits(requests["a"], weights, config)
-    for p in range(70):
-        assert (whole[("a", p)] - cut[("a", p)]).abs().max() < 0.05
-        assert (whole[("a", p)] - truth[p]).abs().max() < 0.1
+    truth = {("a", p): row for p, row in enumerate(toy_plain_logits(requests["a"], weights, config))}
+    yardstick = {("a", p): row for p, row in enumerate(toy_plain_logits(requests["a"], weights, config, torch.bfloat16))}
+    for name, schedule in (("whole", harness.whole_schedule), ("chunks", harness.chunk_schedule)):
+        rows = harness.run_schedule(runner, cache, schedule(requests))
+        harness.assert_rows_close(rows, truth, torch.bfloat16, f"toy bfloat16 {name}", yardstick)
