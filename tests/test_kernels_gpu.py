@@ -247,6 +247,8 @@ MMA_CASES = [c for c in ATTENTION_CASES if c[2] % 16 == 0] + [
     (32, 8, 128, [2100, 64, 640], [2099, 0, 600], 16, 0),
     (20, 1, 48, [700, 400], [699, 330], 5, 0),          # a group of 20 heads: two head chunks per kv head
     (6, 3, 80, [520, 130], [519, 1], 16, 64),
+    (3, 3, 96, [200, 70], [199, 6], 16, 0),             # head sizes between the usual ones: every multiple of 16 is taken
+    (4, 2, 144, [330, 65], [300, 64], 8, 0),
 ]
 
 
