@@ -13,7 +13,7 @@ from ctypes import c_float, c_int, c_void_p
 import numpy as np
 import torch
 
-from . import attention_tc, build
+from . import attention_tc, build, tuning
 from .ops import KernelError, _check, _p, _stream
 
 _libs: dict = {}
@@ -112,7 +112,7 @@ def _slots(head_dim) -> int:
 # wave), 4.92 with 11 to 13; batch 1 is flat from 16 to 43 spans, batch 4 best at 11, batch 16 at 3 or 6.
 # Timed alone, without the projection before it and the chained launches around it, the same pair of
 # kernels prefers fewer, longer spans (256 blocks: two per SM); that did not carry over to the step.
-SPAN_STARTUP, SPAN_MERGE = 2.0, 0.15
+SPAN_STARTUP, SPAN_MERGE = tuning.SPAN_STARTUP_TILES, tuning.SPAN_MERGE_TILES
 
 
 def _span_cost(tiles, n_spans, blocks_per_span, slots) -> float:

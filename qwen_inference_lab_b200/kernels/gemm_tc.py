@@ -11,12 +11,12 @@ from ctypes import c_float, c_int, c_void_p
 import torch
 
 from . import build
-from . import ops
+from . import ops, tuning
 from .ops import KernelError, _check, _need, _p, _stream
 
 _lib = None
 _sm_count = None
-MIN_ROWS = 17
+MIN_ROWS = tuning.TILE_KERNEL_MIN_ROWS
 
 
 def _describe_fault(code):
@@ -79,7 +79,7 @@ def gemm_tc(a, weight, bias=None, residual=None, out=None, silu_pairs=False):
     return out
 
 
-QKV_TAIL_MIN_ROWS = 512      # below this the pair kernel has too few tiles to beat the library product + the tail kernel
+QKV_TAIL_MIN_ROWS = tuning.QKV_TAIL_MIN_ROWS
 
 
 def qkv_tail_usable(a, weight, head_dim, rotary_dim, norm_weights, pages) -> bool:

@@ -11,14 +11,14 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
-from . import build
+from . import build, tuning
 
 F32, BF16 = 0, 1
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "gemm_small_m.cu", "attention_generic.cu",
                 "sampling.cu"]
-SMALL_M_MAX_ROWS = 16
+SMALL_M_MAX_ROWS = min(16, tuning.SMALL_M_MAX_ROWS)      # the kernel takes 16 at most
 
 _core = None
 
@@ -205,7 +205,7 @@ def small_m_ok(a, weight) -> bool:
     as a vocabulary head (measured at 151936 x 4096: 274 us against the library's 211 us) that
     costs more than its epilogues save, so those go to the library.
     """
-    if a.shape[0] > 8 and weight.shape[0] * weight.shape[1] >= (1 << 28):
+    if a.shape[0] > 8 and weight.shape[0] * weight.shape[1] >= tuning.SMALL_M_LIBRARY_ELEMENTS:
         return False
     return (a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and a.shape[0] <= SMALL_M_MAX_ROWS
             and weight.shape[1] % 8 == 0 and a.is_contiguous())
