@@ -71,6 +71,36 @@ def test_temperature_sampling_matches_plain_and_is_reproducible(models):
             sequence.append(token)
 
 
+def test_sampling_settings_live_in_the_requests_slot_and_go_with_it(models):
+    """A request's temperature, seed and draw count sit in its state slot on the device.  Requests that follow one
+    another through the same two rows, some greedy, some sampling, with and without running a step ahead: each gets
+    its own settings, a greedy one never inherits its predecessor's, and the draws are the plain implementation's."""
+    from qwen_inference_lab_b200 import Engine
+    model, weights, cfg = models("B", torch.float32)
+    prompts = [harness.random_tokens(cfg, n, 300 + n) for n in (7, 12, 3, 20, 9, 5)]
+    settings = [dict(temperature=0.9, seed=5), dict(), dict(temperature=0.0, seed=77), dict(temperature=1.4, seed=6),
+                dict(), dict(temperature=0.9, seed=5)]
+    for overlap in (False, True):
+        engine = Engine(model, num_pages=48, page_size=8, token_budget=24, prefill_chunk=8, max_active=2, overlap=overlap)
+        ids = [engine.submit(p, max_new_tokens=7, ignore_eos=True, **kw) for p, kw in zip(prompts, settings)]
+        rows_used = {}
+        while not engine.idle:
+            engine.step()
+            for rid in ids:
+                if rid in engine.cache.rows:
+                    rows_used.setdefault(rid, engine.cache.row(rid))
+        assert sorted(set(rows_used.values())) == [0, 1] and len(rows_used) == 6      # six requests through two rows
+        for rid, prompt, kw in zip(ids, prompts, settings):
+            tokens = engine.result(rid)["token_ids"]
+            sequence = list(prompt)
+            for counter, token in enumerate(tokens):
+                logits = plain.logits(sequence, weights, cfg)[-1]
+                assert token == plain.sample(logits, kw.get("temperature", 0.0), kw.get("seed", 0), counter), \
+                    f"request {rid} (overlap {overlap}) token {counter}"
+                sequence.append(token)
+        assert engine.cache.free_pages() == 48
+
+
 def test_eos_cancel_arrival_and_failure(models, monkeypatch):
     from qwen_inference_lab_b200 import Engine
     model, weights, cfg = models("A", torch.float32)
