@@ -295,13 +295,200 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
     }
 }
 
+// ------------------------------------------------------------------ 32 output features a block
+// The same product with two 16-row weight tiles per block and stages of 256 k-values (row segments of 512 bytes).
+// A run's activation fragments, the norm weight's multiply and the two MMAs for the rows' sums of squares then serve
+// 32 output features instead of 16, so the instructions per weight byte drop by about a third (the kernel above
+// is bound by its instruction stream once the norm is inside), and weights are 78 % of what goes through the ring
+// instead of 64 %.  Whole blocks only (N a multiple of 32); the last, partial stage is zero-filled as above.
+#define GW_ROWS 32
+#define GW_STAGE_K 256
+#define GW_STAGES 4
+#define GW_PIECES (GW_STAGE_K / 8)                 // 16-byte pieces a row segment
+#define GW_PASS_ROWS (GSM_THREADS / GW_PIECES)     // rows one pass of all threads copies
+#define GW_RUNS (GW_STAGE_K / GSM_WARPS / 32)      // runs of 32 k-values per warp and stage
+#define GW_ROW_BYTES (GW_STAGE_K * 2 + 64)         // 576: again 64 mod 128
+
+// Rows [FIRST, LAST) of a stage: thread tid copies piece tid % 32 of rows FIRST + i * 4 + tid / 32.
+template <int FIRST_ROW, int LAST_ROW>
+__device__ __forceinline__ void gw_issue_rows(const bf16* __restrict__ W, const bf16* __restrict__ x, unsigned ring,
+                                              unsigned stage_offset, int n0, int M, int K, int k0, int tid) {
+    const int piece = tid % GW_PIECES, sub = tid / GW_PIECES;
+    const int k = k0 + piece * 8;
+    const bool in_k = k < K;                      // K is a multiple of 8
+#pragma unroll
+    for (int row = FIRST_ROW + sub; row < LAST_ROW; row += GW_PASS_ROWS) {
+        const bool is_w = row < GW_ROWS;
+        const int src_row = is_w ? n0 + row : row - GW_ROWS;
+        if (!is_w && src_row >= M) continue;     // a token past M feeds only its own, unwritten column
+        const bf16* src = (is_w ? W : x) + (size_t)src_row * K + (in_k ? k : 0);
+        gsm_cp16_zfill(ring + stage_offset + row * GW_ROW_BYTES + piece * 16, src, in_k);
+    }
+}
+
+template <int NT, int NORM>
+__global__ void __launch_bounds__(GSM_THREADS)
+gemm_small_m_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const bf16* __restrict__ bias,
+                         const bf16* residual, void* out, const bf16* __restrict__ norm_w, float norm_eps,
+                         int M, int N, int K, int out_f32, int silu_pairs, int first_wave) {
+    extern __shared__ __align__(128) unsigned char ring[];
+    constexpr int XROWS = 8 * NT;
+    constexpr int NORM_ROW = GW_ROWS + XROWS;
+    constexpr int STAGE_BYTES = (GW_ROWS + XROWS + NORM) * GW_ROW_BYTES;
+    constexpr int STAGES = NT == 2 ? GW_STAGES - 1 : GW_STAGES;     // two blocks an SM either way
+    __shared__ float red[GSM_WARPS][GW_ROWS][8 * NT + 1];
+    __shared__ float squares[GSM_WARPS][8 * NT];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * GW_ROWS;
+    const int stages_total = (K + GW_STAGE_K - 1) / GW_STAGE_K;
+    const unsigned ring_address = (unsigned)__cvta_generic_to_shared(ring);
+    auto issue_norm = [&](unsigned offset, int k0) {
+        if (NORM && tid < GW_PIECES) {
+            const int k = k0 + tid * 8;
+            const bool valid = k < K;
+            gsm_cp16_zfill(ring_address + offset + NORM_ROW * GW_ROW_BYTES + tid * 16, norm_w + (valid ? k : 0), valid);
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < stages_total) {
+            gw_issue_rows<0, GW_ROWS>(W, x, ring_address, s * STAGE_BYTES, n0, M, K, s * GW_STAGE_K, tid);
+            issue_norm(s * STAGE_BYTES, s * GW_STAGE_K);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    }
+    if (warp == 0 && (int)blockIdx.x < first_wave) {     // see the kernel above: a little more of each row into L2
+        const long long begin = (long long)(STAGES - 1) * GW_STAGE_K * 2;
+        long long bytes = (long long)K * 2 - begin;
+        if (bytes > GSM_L2_AHEAD / 2) bytes = GSM_L2_AHEAD / 2;
+        bytes &= ~15ll;
+        if (bytes > 0) {
+            const char* row = reinterpret_cast<const char*>(W + (size_t)(n0 + lane) * K) + begin;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(row), "r"((unsigned)bytes) : "memory");
+        }
+    }
+    qil_wait_for_producer();
+    qil_release_consumer();
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < stages_total)
+            gw_issue_rows<GW_ROWS, GW_ROWS + XROWS>(W, x, ring_address, s * STAGE_BYTES, n0, M, K, s * GW_STAGE_K, tid);
+        asm volatile("cp.async.commit_group;\n" ::);
+    }
+    float acc[2][NT][4];
+    float gram[NORM ? NT : 1][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+        for (int rt = 0; rt < 2; ++rt) acc[rt][j][0] = acc[rt][j][1] = acc[rt][j][2] = acc[rt][j][3] = 0.f;
+        if (NORM) gram[j][0] = gram[j][1] = gram[j][2] = gram[j][3] = 0.f;
+    }
+    for (int s = 0; s < stages_total; ++s) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2));
+        __syncthreads();
+        {
+            const int next = s + STAGES - 1;
+            if (next < stages_total) {
+                const unsigned offset = (next % STAGES) * STAGE_BYTES;
+                gw_issue_rows<0, GW_ROWS + XROWS>(W, x, ring_address, offset, n0, M, K, next * GW_STAGE_K, tid);
+                issue_norm(offset, next * GW_STAGE_K);
+            }
+            asm volatile("cp.async.commit_group;\n" ::);
+        }
+        const unsigned char* stage = ring + (s % STAGES) * STAGE_BYTES;
+        const int kw = warp * (GW_STAGE_K / GSM_WARPS);
+#pragma unroll
+        for (int r = 0; r < GW_RUNS; ++r) {
+            const int byte = (kw + r * 32 + 8 * t) * 2;
+            uint4 vx[NT];
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+                vx[j] = *reinterpret_cast<const uint4*>(stage + (GW_ROWS + 8 * j + g) * GW_ROW_BYTES + byte);
+            if (NORM) {
+                const uint4 vn = *reinterpret_cast<const uint4*>(stage + NORM_ROW * GW_ROW_BYTES + byte);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    gsm_mma(gram[j], vx[j].x, 0u, vx[j].y, 0u, vx[j].x, vx[j].y);
+                    gsm_mma(gram[j], vx[j].z, 0u, vx[j].w, 0u, vx[j].z, vx[j].w);
+                    vx[j] = make_uint4(gsm_mul2(vx[j].x, vn.x), gsm_mul2(vx[j].y, vn.y),
+                                       gsm_mul2(vx[j].z, vn.z), gsm_mul2(vx[j].w, vn.w));
+                }
+            }
+#pragma unroll
+            for (int rt = 0; rt < 2; ++rt) {
+                const uint4 va = *reinterpret_cast<const uint4*>(stage + (16 * rt + g) * GW_ROW_BYTES + byte);
+                const uint4 vb = *reinterpret_cast<const uint4*>(stage + (16 * rt + g + 8) * GW_ROW_BYTES + byte);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    gsm_mma(acc[rt][j], va.x, vb.x, va.y, vb.y, vx[j].x, vx[j].y);
+                    gsm_mma(acc[rt][j], va.z, vb.z, va.w, vb.w, vx[j].z, vx[j].w);
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+        for (int rt = 0; rt < 2; ++rt) {
+            red[warp][16 * rt + g][8 * j + 2 * t] = acc[rt][j][0];
+            red[warp][16 * rt + g][8 * j + 2 * t + 1] = acc[rt][j][1];
+            red[warp][16 * rt + g + 8][8 * j + 2 * t] = acc[rt][j][2];
+            red[warp][16 * rt + g + 8][8 * j + 2 * t + 1] = acc[rt][j][3];
+        }
+        if (NORM && t == (g >> 1)) squares[warp][8 * j + g] = (g & 1) ? gram[j][1] : gram[j][0];
+    }
+    __syncthreads();
+    auto inverse_rms = [&](int token) {
+        if (!NORM) return 1.f;
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < GSM_WARPS; ++w) total += squares[w][token];
+        return rsqrtf(total / (float)K + norm_eps);
+    };
+    if (silu_pairs) {
+        // each 16-row tile holds 8 gate features (rows 0..7) and the matching 8 up features (rows 8..15)
+        const int out_width = N / 2;
+        for (int idx = tid; idx < 2 * 8 * 8 * NT; idx += GSM_THREADS) {
+            const int r = idx & 7, rt = (idx >> 3) & 1, token = idx >> 4;
+            const int col = (blockIdx.x * 2 + rt) * 8 + r;
+            if (token >= M || col >= out_width) continue;
+            float gate = 0.f, up = 0.f;
+#pragma unroll
+            for (int w = 0; w < GSM_WARPS; ++w) { gate += red[w][16 * rt + r][token]; up += red[w][16 * rt + r + 8][token]; }
+            const float scale = inverse_rms(token);
+            gate = round_to<bf16>(gate * scale);
+            up = round_to<bf16>(up * scale);
+            const float act = round_to<bf16>(__fdividef(gate, 1.0f + __expf(-gate)));
+            reinterpret_cast<bf16*>(out)[(size_t)token * out_width + col] = __float2bfloat16_rn(act * up);
+        }
+        return;
+    }
+    for (int idx = tid; idx < GW_ROWS * 8 * NT; idx += GSM_THREADS) {
+        const int token = idx / GW_ROWS, r = idx % GW_ROWS;
+        const int n = n0 + r;
+        if (token >= M || n >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < GSM_WARPS; ++w) v += red[w][r][token];
+        v *= inverse_rms(token);
+        if (bias != nullptr) v += __bfloat162float(bias[n]);
+        if (residual != nullptr) v = __bfloat162float(residual[(size_t)token * N + n]) + v;
+        if (out_f32) reinterpret_cast<float*>(out)[(size_t)token * N + n] = v;
+        else reinterpret_cast<bf16*>(out)[(size_t)token * N + n] = __float2bfloat16_rn(v);
+    }
+}
+
 extern "C" int qil_gemm_small_m_max_rows() { return 16; }
 
 // norm_w: null, or the K weights of the RMSNorm to apply to x first (with norm_eps).
 extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, const void* residual, void* out,
                                 const void* norm_w, float norm_eps, int M, int N, int K, int out_f32, int silu_pairs,
-                                cudaStream_t stream) {
+                                int rows_per_block, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
+    if (rows_per_block != 16 && rows_per_block != 32) QIL_REFUSE("gemm_small_m: %d output features a block; 16 or 32", rows_per_block);
+    if (rows_per_block == 32 && N % 32) QIL_REFUSE("gemm_small_m: 32 output features a block need N %% 32 == 0, got %d", N);
     if (M > 16) QIL_REFUSE("gemm_small_m: %d rows; this kernel takes at most 16", M);
     if (K <= 0 || K % 8) QIL_REFUSE("gemm_small_m: K %d must be a positive multiple of 8", K);
     if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)norm_w) & 15)
@@ -325,6 +512,32 @@ extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, 
         for (int i = 0; i < 4; ++i)
             if (e[i] != cudaSuccess) QIL_REFUSE("gemm_small_m: cannot reserve %d bytes of shared memory", smem1n);
         configured = true;
+    }
+    if (rows_per_block == 32) {
+        const int w1 = GW_STAGES * (GW_ROWS + 8) * GW_ROW_BYTES, w1n = GW_STAGES * (GW_ROWS + 8 + 1) * GW_ROW_BYTES;
+        const int w2 = (GW_STAGES - 1) * (GW_ROWS + 16) * GW_ROW_BYTES, w2n = (GW_STAGES - 1) * (GW_ROWS + 16 + 1) * GW_ROW_BYTES;
+        static bool wide_configured = false;
+        if (!wide_configured) {
+            cudaError_t e[4] = {
+                cudaFuncSetAttribute(gemm_small_m_wide_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, w1),
+                cudaFuncSetAttribute(gemm_small_m_wide_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, w2),
+                cudaFuncSetAttribute(gemm_small_m_wide_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, w1n),
+                cudaFuncSetAttribute(gemm_small_m_wide_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, w2n)};
+            for (int i = 0; i < 4; ++i)
+                if (e[i] != cudaSuccess) QIL_REFUSE("gemm_small_m: cannot reserve %d bytes of shared memory", w2n);
+            wide_configured = true;
+        }
+#define GW_LAUNCH(NT, NORM, SMEM)                                                                                   \
+        qil_launch_chained(gemm_small_m_wide_kernel<NT, NORM>, dim3(N / GW_ROWS), dim3(GSM_THREADS), SMEM, stream,  \
+                           (const bf16*)x, (const bf16*)W, (const bf16*)bias, (const bf16*)residual, out,            \
+                           (const bf16*)norm_w, norm_eps, M, N, K, out_f32, silu_pairs, first_wave)
+        if (norm_w == nullptr) {
+            if (M <= 8) GW_LAUNCH(1, 0, w1); else GW_LAUNCH(2, 0, w2);
+        } else {
+            if (M <= 8) GW_LAUNCH(1, 1, w1n); else GW_LAUNCH(2, 1, w2n);
+        }
+#undef GW_LAUNCH
+        QIL_CHECK_LAUNCH();
     }
 #define GSM_LAUNCH(NT, NORM, SMEM)                                                                                  \
     qil_launch_chained(gemm_small_m_kernel<NT, NORM>, dim3(blocks), dim3(GSM_WARPS * 32), SMEM, stream,           \

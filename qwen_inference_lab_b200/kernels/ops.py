@@ -212,13 +212,15 @@ def small_m_ok(a, weight) -> bool:
 
 
 def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=False, silu_pairs=False,
-                 norm_weight=None, norm_eps=0.0):
+                 norm_weight=None, norm_eps=0.0, rows_per_block=None):
     """out = a @ weight.T (+ bias) (+ residual) for a decode step's few rows, streaming the weight once.
 
     a bfloat16 [M <= 16, K]; weight bfloat16 [N, K].  ``out_float32`` returns float32 (the LM head).
     ``silu_pairs``: weight rows are groups of [8 gate, 8 up]; returns silu(gate) * up, bfloat16 [M, N/2].
     ``residual`` may be ``out`` itself.  With ``norm_weight`` (bfloat16 [K]) the kernel first applies
     RMSNorm(a; norm_weight, norm_eps): the product of the normed rows, with no pass of its own over them.
+    ``rows_per_block``: 16 or 32 output features a block (32 wants N a multiple of 32); None leaves it to the
+    measured rule in ``tuning``.  The two forms add a product's terms in different orders.
     """
     _need(a, "a", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
     m, k = a.shape
@@ -242,10 +244,15 @@ def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=Fals
         _need(norm_weight, "norm_weight", torch.bfloat16, 1)
         if norm_weight.shape[0] != k:
             raise KernelError("gemm_small_m: the norm weight must have one value per input feature")
+    if rows_per_block is None:
+        wide = (n % 32 == 0 and n // 32 >= tuning.SMALL_M_WIDE_MIN_BLOCKS
+                and (m > 8 or n * k < tuning.SMALL_M_WIDE_MAX_ELEMENTS))
+        rows_per_block = 32 if wide else 16
     lib = core()
     _check(lib, lib.qil_gemm_small_m(_p(a), _p(weight), _p(bias), _p(residual), _p(out), _p(norm_weight),
                                      c_float(float(norm_eps)), c_int(m), c_int(n), c_int(k),
-                                     c_int(1 if out_float32 else 0), c_int(1 if silu_pairs else 0), _stream()),
+                                     c_int(1 if out_float32 else 0), c_int(1 if silu_pairs else 0),
+                                     c_int(rows_per_block), _stream()),
            "gemm_small_m")
     return out
 

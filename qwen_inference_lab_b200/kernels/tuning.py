@@ -22,6 +22,13 @@ SMALL_M_MAX_ROWS = _tuned("SMALL_M_MAX_ROWS", 16)
 #: least this many elements it then loses to the library (151936 x 4096 vocabulary head, 16 rows: 274 us
 #: against 211 us).
 SMALL_M_LIBRARY_ELEMENTS = _tuned("SMALL_M_LIBRARY_ELEMENTS", 1 << 28)
+#: With at most 8 rows the decode product gives a block 32 output features instead of 16 when that still leaves
+#: this many blocks (one for each of the 148 SMs: 4096 features make 128 and lose, 19.7 -> 22.9 us at K 12288)
+#: and the matrix has fewer than this many elements (a stream as long as a vocabulary head's runs 3 % faster on
+#: the longer row segments of the 16-feature blocks: 194.7 against 200.9 us).  In between the wider block wins by
+#: its fewer instructions per weight byte (6144 x 4096 with the norm: 20.3 -> 18.5 us; 24576 x 4096: 37.2 -> 36.2).
+SMALL_M_WIDE_MIN_BLOCKS = _tuned("SMALL_M_WIDE_MIN_BLOCKS", 148)
+SMALL_M_WIDE_MAX_ELEMENTS = _tuned("SMALL_M_WIDE_MAX_ELEMENTS", 1 << 28)
 #: From this many rows on the gate/up product runs on the tcgen05 tile kernel (the first row count the decode
 #: product does not take).
 TILE_KERNEL_MIN_ROWS = _tuned("TILE_KERNEL_MIN_ROWS", 17)

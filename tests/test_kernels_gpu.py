@@ -528,6 +528,50 @@ def test_gemm_small_m_with_gate_epilogue_and_paired_silu(m, inner, k):
           torch.nn.functional.silu(gate.float()) * up.float(), torch.float32, scale=2)
 
 
+@pytest.mark.parametrize("m,n,k,eps", [(1, 32, 8, 1e-6), (5, 320, 1000, 1e-5), (8, 4768, 264, 1e-6), (12, 96, 520, 3e-6),
+                                       (16, 64, 4096, 1e-6)])
+def test_gemm_small_m_with_32_features_a_block(m, n, k, eps):
+    """The form with two weight tiles a block (what wide matrices get; forced here at small ones too): every
+    epilogue against float64, and against the 16-feature form, whose sums differ only in their order."""
+    from qwen_inference_lab_b200.kernels import tuning
+    torch.manual_seed(15)
+    a = (torch.randn(m, k) * torch.logspace(-1, 1, m).unsqueeze(1)).to(torch.bfloat16)
+    norm_w = (1 + torch.randn(k) * 0.3).to(torch.bfloat16)
+    w = (torch.randn(n, k) * 0.1).to(torch.bfloat16)
+    bias = (torch.randn(n) * 0.1).to(torch.bfloat16)
+    residual = torch.randn(m, n).to(torch.bfloat16)
+    product = a.double() @ w.double().t()
+    normed = a.double() * torch.rsqrt(a.double().pow(2).mean(-1, keepdim=True) + eps) * norm_w.double()
+    normed_product = normed @ w.double().t()
+    wide = lambda **kw: ops().gemm_small_m(a.cuda(), w.cuda(), rows_per_block=32, **kw)
+    narrow = lambda **kw: ops().gemm_small_m(a.cuda(), w.cuda(), rows_per_block=16, **kw)
+    scale = max(4.0, float(product.abs().max()) / 4)
+    close(wide(bias=bias.cuda(), residual=residual.cuda()), (product + bias.double() + residual.double()).float(),
+          torch.bfloat16, scale=scale)
+    exact = wide(out_float32=True)
+    torch.testing.assert_close(exact.cpu(), product.float(), atol=1e-4 * scale, rtol=1e-4)
+    torch.testing.assert_close(exact, narrow(out_float32=True), atol=1e-4 * scale, rtol=1e-4)
+    with_norm = wide(norm_weight=norm_w.cuda(), norm_eps=eps, out_float32=True)
+    torch.testing.assert_close(with_norm.cpu(), normed_product.float(), atol=0.03 * float(normed_product.abs().max()) / 4,
+                               rtol=0.02)
+    torch.testing.assert_close(with_norm, narrow(norm_weight=norm_w.cuda(), norm_eps=eps, out_float32=True),
+                               atol=1e-3 * float(normed_product.abs().max()), rtol=1e-3)
+    half = normed_product.float().view(m, n // 16, 2, 8)
+    expected = torch.nn.functional.silu(half[:, :, 0]) * half[:, :, 1]
+    close(wide(norm_weight=norm_w.cuda(), norm_eps=eps, silu_pairs=True), expected.reshape(m, n // 2), torch.bfloat16,
+          scale=max(2.0, float(expected.abs().max()) / 2))
+    buffer = residual.cuda().clone()
+    ops().gemm_small_m(a.cuda(), w.cuda(), residual=buffer, out=buffer, rows_per_block=32)
+    close(buffer, (product + residual.double()).float(), torch.bfloat16, scale=scale)
+    alone = ops().gemm_small_m(a[-1:].cuda().contiguous(), w.cuda(), out_float32=True, rows_per_block=32)
+    assert torch.equal(alone.cpu()[0], exact.cpu()[-1])
+    # left to itself the face takes this form from 148 blocks of 32 features on
+    chosen = ops().gemm_small_m(a.cuda(), w.cuda(), out_float32=True)
+    assert torch.equal(chosen, exact if n // 32 >= tuning.SMALL_M_WIDE_MIN_BLOCKS else narrow(out_float32=True))
+    with pytest.raises(Exception, match="32"):
+        ops().gemm_small_m(a.cuda(), w[:n - 16].contiguous().cuda(), rows_per_block=32)
+
+
 @pytest.mark.parametrize("m,n,k", [(17, 8, 8), (128, 256, 64), (100, 264, 200), (300, 520, 1000), (2048, 1024, 4096)])
 def test_gemm_tensor_memory(m, n, k):
     """The tcgen05/TMA kernel: plain, with bias and residual, in place, at sizes that are no multiple of a tile."""
