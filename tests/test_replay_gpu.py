@@ -231,3 +231,30 @@ def test_long_prompts_take_the_tensor_memory_kernels(folders, monkeypatch):
     lengths = [len(tokens) for tokens in requests.values()]
     assert calls["qkv"] == sum(n >= gemm_tc.QKV_TAIL_MIN_ROWS for n in lengths) * layers == 3 * layers
     assert calls["gate_up"] == len(lengths) * layers and calls["attention"] == len(lengths) * layers
+
+
+def test_decoding_with_32_feature_blocks_in_the_products(folders, monkeypatch):
+    """The decode product's form with two weight tiles a block is chosen by the width of the matrix, which no tiny
+    configuration reaches: here every product whose width is a multiple of 32 is made to take it (q/k/v of tiny D with
+    its bias and the norm inside, gate/up of tiny C with the activation behind, every product of tiny A down to the
+    float32 head), in single-token steps against the plain rows."""
+    from qwen_inference_lab_b200.kernels import ops, tuning
+    monkeypatch.setattr(tuning, "SMALL_M_WIDE_MIN_BLOCKS", 1)
+    taken = {16: 0, 32: 0}
+    original = ops.core().qil_gemm_small_m
+    def counted(*args):
+        taken[args[12].value] += 1
+        return original(*args)
+    monkeypatch.setattr(ops.core(), "qil_gemm_small_m", counted)
+    for case in ("D", "C", "A"):
+        folder, weights, requests = folders[case]
+        cfg, page_size = CASES[case]["cfg"], CASES[case]["page_size"]
+        schedule = harness.tail_decode_schedule(requests, tail=12)
+        num_pages = harness.peak_pages(schedule, page_size) + 1
+        _, cache, runner = harness.build_engine_parts(folder, torch.bfloat16, num_pages=num_pages, page_size=page_size)
+        actual = harness.run_schedule(runner, cache, schedule)
+        expected = harness.plain_rows(requests, weights, cfg, torch.float32)
+        yardstick = harness.plain_rows(requests, weights, cfg, torch.bfloat16)
+        harness.assert_rows_close(actual, {k: expected[k] for k in actual}, torch.bfloat16, f"tiny {case}, wide blocks",
+                                  {k: yardstick[k] for k in actual})
+    assert taken[32] > 0 and taken[16] > 0
