@@ -46,6 +46,15 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool va
     const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are filled with zeros
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
 }
+// The same for bytes that are read once a step (a single token's keys and values): they are the first to leave L2,
+// so that what is read again (activations, partial sums, tables) stays.
+__device__ __forceinline__ void cp_async16_stream(void* smem, const void* gmem, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;
+    unsigned long long policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n" ::"r"(dst), "l"(gmem), "r"(bytes), "l"(policy));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
@@ -511,7 +520,7 @@ __device__ __forceinline__ void attn_decode_span_block(
             const int row = idx / CPR, piece = idx % CPR;
             const int off = __shfl_sync(0xffffffffu, offset_of_lane, row);
             const bool valid = off >= 0;
-            cp_async16(dst + row * LDS + piece * 8, p.kv + (size_t)(valid ? off : 0) * 8 + piece * 8 + (valid ? plane : 0), valid);
+            cp_async16_stream(dst + row * LDS + piece * 8, p.kv + (size_t)(valid ? off : 0) * 8 + piece * 8 + (valid ? plane : 0), valid);
         }
     };
     bf16* const my_k = sK + warp * 16 * LDS;    // this warp's rows of buffer 0; buffer 1 lies KV_TILE rows further

@@ -61,6 +61,22 @@ struct GsmCopy {
     bool short_path;    // all 16 weight rows of the block exist
 };
 
+// Weights are read once a step and there are far more of them than L2 holds: their copies carry the policy
+// "first to leave L2", so that what is read again (activations, partial sums, tables) stays.  Measured on the
+// Qwen3-8B decode step, together with the same hint on the single-token attention's keys and values: 4.65 -> 4.61 ms
+// at batch 8, 3.24 -> 3.21 at batch 1.
+__device__ __forceinline__ unsigned long long gsm_stream_policy() {
+    unsigned long long policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void gsm_cp16_stream(unsigned dst, const void* src, unsigned long long policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "l"(policy));
+}
+__device__ __forceinline__ void gsm_cp16_zfill_stream(unsigned dst, const void* src, bool valid, unsigned long long policy) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n" ::"r"(dst), "l"(src), "r"(bytes), "l"(policy));
+}
 __device__ __forceinline__ void gsm_cp16(unsigned dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
 }
@@ -85,7 +101,7 @@ __device__ __forceinline__ void gsm_issue_rows(const GsmCopy& c, unsigned stage_
 #pragma unroll
         for (int row2 = FIRST_ROW; row2 < LAST_ROW; row2 += GSM_PASS_ROWS) {
             if (row2 < GSM_ROWS) {
-                gsm_cp16(dst + row2 * GSM_ROW_BYTES, w + (size_t)row2 * c.K);
+                gsm_cp16_stream(dst + row2 * GSM_ROW_BYTES, w + (size_t)row2 * c.K, gsm_stream_policy());
             } else if (row2 - GSM_ROWS + half < c.M) {    // a token past M feeds only its own, unwritten column
                 gsm_cp16(dst + row2 * GSM_ROW_BYTES, xs + (size_t)(row2 - GSM_ROWS) * c.K);
             }
@@ -101,7 +117,8 @@ __device__ __forceinline__ void gsm_issue_rows(const GsmCopy& c, unsigned stage_
         const int src_row = is_w ? c.n0 + row : row - GSM_ROWS;
         const bool valid = (k < c.K) && (is_w ? src_row < c.N : src_row < c.M);   // K is a multiple of 8
         const bf16* src = (is_w ? c.W : c.x) + (size_t)(valid ? src_row : 0) * c.K + (valid ? k : 0);
-        gsm_cp16_zfill(c.ring + stage_offset + row * GSM_ROW_BYTES + piece * 16, src, valid);
+        if (is_w) gsm_cp16_zfill_stream(c.ring + stage_offset + row * GSM_ROW_BYTES + piece * 16, src, valid, gsm_stream_policy());
+        else gsm_cp16_zfill(c.ring + stage_offset + row * GSM_ROW_BYTES + piece * 16, src, valid);
     }
 }
 
@@ -322,7 +339,8 @@ __device__ __forceinline__ void gw_issue_rows(const bf16* __restrict__ W, const 
         const int src_row = is_w ? n0 + row : row - GW_ROWS;
         if (!is_w && src_row >= M) continue;     // a token past M feeds only its own, unwritten column
         const bf16* src = (is_w ? W : x) + (size_t)src_row * K + (in_k ? k : 0);
-        gsm_cp16_zfill(ring + stage_offset + row * GW_ROW_BYTES + piece * 16, src, in_k);
+        if (is_w) gsm_cp16_zfill_stream(ring + stage_offset + row * GW_ROW_BYTES + piece * 16, src, in_k, gsm_stream_policy());
+        else gsm_cp16_zfill(ring + stage_offset + row * GW_ROW_BYTES + piece * 16, src, in_k);
     }
 }
 
