@@ -73,6 +73,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, 
                  ::"r"(smem_u32(smem)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
 
+// The same with the hint that these bytes are the first to leave L2: a weight tile that only one tile of tokens reads
+// (a product of at most 128 rows) is read once a step.
+__device__ __forceinline__ void tma_load_2d_stream(void* smem, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
+    unsigned long long policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;\n"
+                 ::"r"(smem_u32(smem)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy) : "memory");
+}
+
 // Shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte swizzle, groups of 8
 // rows 1024 bytes apart (the layout a TMA load with CU_TENSOR_MAP_SWIZZLE_128B writes).
 __device__ __forceinline__ unsigned long long umma_desc(unsigned smem_addr) {
@@ -320,7 +329,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     mbar_arrive_expect_tx(&sh->full[stage], TC_STAGE_BYTES);
                     unsigned char* a_dst = tiles + stage * TC_STAGE_BYTES;
                     tma_load_2d(a_dst, &map_a, &sh->full[stage], kb * TC_BK, m0);
-                    tma_load_2d(a_dst + TC_A_BYTES, &map_w, &sh->full[stage], kb * TC_BK, n0);
+                    if (tiles_m == 1) tma_load_2d_stream(a_dst + TC_A_BYTES, &map_w, &sh->full[stage], kb * TC_BK, n0);
+                    else tma_load_2d(a_dst + TC_A_BYTES, &map_w, &sh->full[stage], kb * TC_BK, n0);
                     if (++stage == TC_STAGES) { stage = 0; phase ^= 1; }
                 }
             }
