@@ -75,3 +75,24 @@ def test_two_real_layers_whole_prompts_then_single_tokens(real_folder, monkeypat
         del runner, cache
         torch.cuda.empty_cache()
     assert forms[32] > 0 and forms[16] > 0      # q/k/v and gate/up took the wide form, o and down the other (later steps replay)
+
+
+def test_two_real_layers_long_prompts(real_folder):
+    """Prompts long enough for the tensor-memory kernels at real head counts (the q/k/v product with its fused tail
+    from 512 rows on, the paired gate/up product, whole 128-token attention tiles and what they leave over), whole and
+    cut after 384 tokens, against the plain rows at a few positions."""
+    folder, weights = real_folder
+    requests = {"a": harness.random_tokens(REAL, 640, 5), "b": harness.random_tokens(REAL, 530, 6)}
+    wants = {"a": [0, 127, 128, 400, 639], "b": [1, 255, 256, 511, 529]}
+    whole = [([(rid, tokens, wants[rid])], [rid]) for rid, tokens in requests.items()]
+    cut = [([("a", requests["a"][:384], [0, 127, 128]), ("b", requests["b"][:2], [1])], []),
+           ([("a", requests["a"][384:], [400 - 384, 639 - 384]), ("b", requests["b"][2:], [253, 254, 509, 527])], ["a", "b"])]
+    wanted = {(rid, position) for rid in requests for position in wants[rid]}
+    expected = {k: v for k, v in harness.plain_rows(requests, weights, REAL, torch.float32).items() if k in wanted}
+    yardstick = {k: v for k, v in harness.plain_rows(requests, weights, REAL, torch.bfloat16).items() if k in wanted}
+    for name, schedule in (("whole", whole), ("cut", cut)):
+        _, cache, runner = harness.build_engine_parts(folder, torch.bfloat16, num_pages=80, page_size=16)
+        actual = harness.run_schedule(runner, cache, schedule)
+        harness.assert_rows_close(actual, expected, torch.bfloat16, f"two real layers, long prompts, {name}", yardstick)
+        del runner, cache
+        torch.cuda.empty_cache()
