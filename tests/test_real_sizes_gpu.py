@@ -96,3 +96,22 @@ def test_two_real_layers_long_prompts(real_folder):
         harness.assert_rows_close(actual, expected, torch.bfloat16, f"two real layers, long prompts, {name}", yardstick)
         del runner, cache
         torch.cuda.empty_cache()
+
+
+def test_two_real_layers_sixty_four_requests_decoding_together(real_folder):
+    """64 short requests that decode side by side: products of 64 rows (the library's and the tile kernel's), the
+    single-token attention with a merge kernel behind it (a span's worth of blocks fills the GPU), recorded graphs."""
+    folder, weights = real_folder
+    requests = {f"r{i}": harness.random_tokens(REAL, 12 + (i * 7) % 19, 100 + i) for i in range(64)}
+    tail = 3
+    schedule = [([(rid, tokens[:-tail], []) for rid, tokens in requests.items()], [])]
+    for i in range(tail):
+        schedule.append(([(rid, [tokens[len(tokens) - tail + i]], [0]) for rid, tokens in requests.items()],
+                         list(requests) if i == tail - 1 else []))
+    wanted = {(rid, position) for rid, tokens in requests.items() for position in range(len(tokens) - tail, len(tokens))}
+    expected = {k: v for k, v in harness.plain_rows(requests, weights, REAL, torch.float32).items() if k in wanted}
+    yardstick = {k: v for k, v in harness.plain_rows(requests, weights, REAL, torch.bfloat16).items() if k in wanted}
+    _, cache, runner = harness.build_engine_parts(folder, torch.bfloat16, num_pages=200, page_size=16, max_requests=64)
+    actual = harness.run_schedule(runner, cache, schedule)
+    assert runner._graphs, "the single-token steps should have been recorded"
+    harness.assert_rows_close(actual, expected, torch.bfloat16, "two real layers, 64 requests", yardstick)
