@@ -102,14 +102,23 @@ def init_random(model, seed, *, device, dtype, storage=None) -> None:
     model.finalize(device, dtype)
 
 
-def write_model_folder(config, seed, directory, *, storage=torch.bfloat16) -> Path:
-    """Write ``config.json`` and ``model.safetensors`` for ``config`` (a typed configuration)."""
+def write_model_folder(config, seed, directory, *, storage=torch.bfloat16, device=None) -> Path:
+    """Write ``config.json`` and ``model.safetensors`` for ``config`` (a typed configuration).
+
+    The values are the same bits wherever they are drawn, so they are drawn on the GPU when there is one
+    (``device=None``) and brought back tensor by tensor: a model of a billion parameters takes the host a minute."""
     directory = Path(directory)
     directory.mkdir(parents=True, exist_ok=True)
     data = config.to_dict()
     entry = registry.lookup(data)
     model = entry.build(config)
+    if device is None:
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+    tensors, done = {}, set()
+    for name, param in model.all_named_params().items():
+        if id(param) not in done:
+            done.add(id(param))
+            tensors[name] = draw(param, seed, name, device=device, dtype=storage).cpu()
     (directory / "config.json").write_text(json.dumps(data, indent=2) + "\n")
-    write_safetensors(directory / "model.safetensors", random_state(model, seed, dtype=storage),
-                      metadata={"format": "pt", "seed": seed})
+    write_safetensors(directory / "model.safetensors", tensors, metadata={"format": "pt", "seed": seed})
     return directory

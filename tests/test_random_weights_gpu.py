@@ -29,7 +29,7 @@ def test_a_model_drawn_on_the_device_is_the_model_of_the_written_folder(tmp_path
     from qwen_inference_lab_b200.weights import SafetensorsFile, write_model_folder
     config = typed(cfg)
     drawn = Qwen3.random(config, seed, dtype=dtype)
-    folder = write_model_folder(config, seed, tmp_path / "model",
+    folder = write_model_folder(config, seed, tmp_path / "model", device="cpu",      # the host's draw against the device's
                                 storage=torch.float32 if dtype == torch.float32 else torch.bfloat16)
     loaded = Qwen3.from_directory(folder, dtype=dtype)
     stacked_a, stacked_b = drawn.layers[-1].mixer.qkv._weight(), loaded.layers[-1].mixer.qkv._weight()
